@@ -1,0 +1,647 @@
+#!/usr/bin/env python
+"""Benchmark of the ELLPACK hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic
+input.  Workloads (the five benchmark configurations):
+
+  cfg5_spmm  (default)  skewed SpMM 262144 x 65536, power-law rows (mean 64, max 2048), C = 1024;
+                        the largest single-GPU SpMM configuration.  N > 1: rows of E split over
+                        the ranks, X replicated, Y stays row-sharded (strong scaling, no
+                        collective in `value`); the NCCL all-gather of Y is timed separately.
+  cfg1_spmm / cfg1_spmv 4096^2, p = 0.1 (C = 256 for SpMM).  Fits in L2, so L2 is flushed
+                        between timed iterations.
+  cfg2_spmv             square iid matrix, --size in {4096,16384,65536}, --sparsity.
+  cfg3_mlp              sparse MLP 4096-4096-4096-4096-1000, batch 256, via SparseOnnxModel
+                        (N > 1: batch-sharded, no collective; --tp: row-sharded + all-gather).
+  cfg4_conv             sparse 3x3 conv 256->256, 56x56, batch 32, [C,H,W,B] layout.
+
+`value` is measured with operands resident in HBM; `e2e` is the same metric through the
+host-buffer entry points (pinned host memory, copies inside the timed region).
+`--impl reference` times the reference's own CPU implementation (oracle/_ref, else the C port)
+on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "sparse-ops_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+L2_FLUSH_BYTES = 512 << 20
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg5_spmm",
+                    choices=["cfg5_spmm", "cfg1_spmm", "cfg1_spmv", "cfg2_spmv", "cfg3_mlp", "cfg4_conv"])
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (testing only)")
+    ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
+    ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
+    ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------------
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def recorded_traffic(kernel: str, workload: str):
+    """DRAM bytes per launch from the committed ncu summary, if one exists for this workload."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(f"{kernel}:{workload}")
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read only)."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+                 "hw_thermal_slowdown": 0x40, "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def _count_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# Taken once at start-up: OpenMP thread binding later narrows the main thread's affinity mask.
+_HOST_CORES = _count_cores()
+
+
+def host_cores():
+    return _HOST_CORES
+
+
+# ------------------------------------------------------------------------------------------------
+# workload construction (host side, seeded)
+# ------------------------------------------------------------------------------------------------
+def build_workload(args, rank: int, world: int):
+    """Returns a dict describing this rank's share: CSR rows, dense operands, byte/flop counts."""
+    import workloads as wl
+    s = args.scale
+    w = args.workload
+    if w == "cfg5_spmm":
+        m = max(4096 * world, int(262144 * s) // (4096 * world) * 4096 * world)
+        n = max(1024, int(65536 * s))
+        C = max(16, int(1024 * s) // 4 * 4)
+        kmax = min(2048, n // 2)
+        per = m // world
+        rowptr, col, val = wl.cfg5_rows(rank * per, per, n=n, kmax=kmax, mean=64.0 if kmax >= 512 else kmax / 8)
+        X = wl.cfg5_dense_operand(n, C)
+        return dict(kind="spmm", m=m, n=n, C=C, rows=per, row0=rank * per, csr=(rowptr, col, val), X=X, bias=None,
+                    desc=f"skewed SpMM {m}x{n}, power-law rows (mean 64, max {kmax}), C={C}")
+    if w in ("cfg1_spmm", "cfg1_spmv"):
+        d = wl.cfg1(s)
+        m = d["m"]
+        per = (m + world - 1) // world
+        lo, hi = min(m, rank * per), min(m, (rank + 1) * per)
+        csr = wl.csr_from_blocks([(0, d["W"][lo:hi])], hi - lo)
+        if w == "cfg1_spmm":
+            return dict(kind="spmm", m=m, n=d["n"], C=d["C"], rows=hi - lo, row0=lo, csr=csr, X=d["X"],
+                        bias=d["bias"][lo:hi].copy(), dense_rows=d["W"][lo:hi],
+                        desc=f"SpMM {m}x{d['n']} iid p=0.1, C={d['C']}, bias")
+        return dict(kind="spmv", m=m, n=d["n"], C=1, rows=hi - lo, row0=lo, csr=csr, x=d["x"],
+                    bias=d["bias"][lo:hi].copy(), desc=f"SpMV {m}x{d['n']} iid p=0.1, bias")
+    if w == "cfg2_spmv":
+        size = max(256, int(args.size * s))
+        d = wl.cfg2_case(size, args.sparsity) if s == 1.0 else None
+        if d is None:
+            p = 1.0 - args.sparsity
+            rp, col, val = wl.csr_from_blocks(wl.bernoulli_matrix(43, size, size, p, 1.0 / np.sqrt(max(1.0, p * size))), size)
+            g = np.random.default_rng(43)
+            d = dict(m=size, n=size, rowptr=rp, col=col, val=val, x=g.uniform(-1, 1, size).astype(np.float32),
+                     bias=g.standard_normal(size).astype(np.float32))
+        m = d["m"]
+        per = (m + world - 1) // world
+        lo, hi = min(m, rank * per), min(m, (rank + 1) * per)
+        rp = d["rowptr"]
+        a, b = int(rp[lo]), int(rp[hi])
+        csr = ((rp[lo:hi + 1] - rp[lo]).astype(np.uint64), d["col"][a:b], d["val"][a:b])
+        return dict(kind="spmv", m=m, n=d["n"], C=1, rows=hi - lo, row0=lo, csr=csr, x=d["x"], bias=d["bias"][lo:hi].copy(),
+                    desc=f"SpMV {m}x{m} iid sparsity {args.sparsity}, bias")
+    if w == "cfg3_mlp":
+        d = wl.cfg3(s)
+        return dict(kind="mlp", **d, desc=f"sparse MLP {'-'.join(map(str, d['dims']))}, 90% sparse, batch {d['B']}")
+    if w == "cfg4_conv":
+        d = wl.cfg4(s, layers=1)
+        return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, [C,H,W,B]")
+    raise SystemExit(f"unknown workload {w}")
+
+
+def spmm_bytes(nnz, m, n, C, bias):
+    return 8 * nnz + 4 * m + (4 * m if bias else 0) + 4 * n * C + 4 * m * C
+
+
+def spmv_bytes(nnz, m, n):
+    return 8 * nnz + 4 * n + 12 * m
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference / CPU arm
+# ------------------------------------------------------------------------------------------------
+def cpu_engine():
+    """(engine, kind): the unmodified reference build when usable here, else the C port."""
+    os.environ.setdefault("OMP_NUM_THREADS", str(host_cores()))
+    os.environ.setdefault("OMP_PLACES", "cores")
+    os.environ.setdefault("OMP_PROC_BIND", "spread")
+    import oracle
+    if oracle.reference_available():
+        try:
+            return oracle.Reference(), "reference"
+        except Exception:
+            pass
+    return oracle.Oracle(), "port"
+
+
+def cpu_sample_runner(args, wk, budget_rows=None):
+    """Builds the bounded CPU sample of this workload.  Returns (run_fn, work_fraction, text)."""
+    import oracle
+    import workloads as wl
+    eng, kind = cpu_engine()
+    is_ref = kind == "reference"
+
+    def make_ell(rowptr, col, val, m, n):
+        Wd, idx, nnz = wl.csr_to_ell(m, rowptr, col, val)
+        E = oracle.EllArrays(m, n, Wd.shape[1], Wd, idx, nnz)
+        return eng.from_arrays(E) if is_ref else E
+
+    if wk["kind"] in ("spmm", "spmv"):
+        rowptr, col, val = wk["csr"]
+        rows = wk["rows"]
+        total_nnz = int(rowptr[-1])
+        take = rows
+        if wk["kind"] == "spmm":
+            # about 4 GFLOP of the same matrix: enough for a stable CPU timing, seconds not minutes
+            target = 4e9 / (2.0 * wk["C"])
+            if total_nnz > target:
+                take = max(1, int(np.searchsorted(rowptr, target)))
+        take = min(take, rows)
+        sub = (rowptr[:take + 1].copy(), col[:int(rowptr[take])], val[:int(rowptr[take])])
+        E = make_ell(*sub, take, wk["n"])
+        frac = float(rowptr[take]) / max(1, total_nnz)
+        bias = None if wk["bias"] is None else wk["bias"][:take].copy()
+        if wk["kind"] == "spmm":
+            X = wk["X"]
+            Y = np.empty((take, wk["C"]), np.float32)
+            run = (lambda: eng.matmul(E, X, bias, out=Y)) if is_ref else (lambda: eng.spmm(E, X, bias))
+        else:
+            x = wk["x"]
+            y = np.empty(take, np.float32)
+            run = (lambda: eng.matvec(E, x, bias, out=y)) if is_ref else (lambda: eng.spmv(E, x, bias))
+        return run, frac, kind, f"rows 0..{take - 1} of {rows} of the same matrix ({frac:.3f} of the nonzeros), full dense operand"
+    if wk["kind"] == "mlp":
+        import onnx_wire
+        import tempfile
+        B = wk["B"]
+        x_mem = np.ascontiguousarray(wk["x"].T)
+        if is_ref:
+            f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+            f.write(onnx_wire.mlp_model(wk["weights"], wk["biases"], wk["acts"], B))
+            f.close()
+            h = eng.model_load(f.name)
+            os.unlink(f.name)
+            return (lambda: eng.model_run(h, x_mem, B)), 1.0, kind, "the whole forward pass (SparseOnnxModel::run of the reference)"
+        Es = [eng.encode(W) for W in wk["weights"]]
+
+        def run():
+            a = x_mem
+            for E, b, act in zip(Es, wk["biases"], (1, 1, 1, 2)):
+                a = eng.spmm(E, a, b, act=1) if act == 1 else eng.activation(eng.spmm(E, a, b), act)
+            return a
+        return run, 1.0, kind, "the whole forward pass (layer loop over the C port)"
+    if wk["kind"] == "conv":
+        B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
+        Bs = max(1, min(B, 4))      # a few images of the batch: the explicit-im2col CPU path is slow
+        g = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+        x_pf = np.ascontiguousarray(wk["x_nchw"][:Bs].transpose(1, 2, 3, 0))
+        if is_ref:
+            h = eng.conv_create(wk["weights"][0], g, wk["biases"][0], True)
+            out = np.empty((Cc, H, W, Bs), np.float32)
+            return (lambda: eng.conv_run(h, 0, x_pf, Bs, Cc, out=out)), Bs / B, kind, \
+                f"{Bs} of {B} images, conv2d_patchmajor_tiled of the reference"
+        E = eng.encode(wk["weights"][0].reshape(Cc, -1))
+        return (lambda: eng.conv2d(E, g, 0, x_pf, Bs, wk["biases"][0], 1)), Bs / B, kind, f"{Bs} of {B} images, C port"
+    raise SystemExit("no CPU sample for this workload")
+
+
+def time_cpu(run, repeats, warmup=1, budget_s=25.0):
+    for _ in range(warmup):
+        run()
+    ts = []
+    t_start = time.perf_counter()
+    for _ in range(max(1, repeats)):
+        t0 = time.perf_counter()
+        run()
+        ts.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    return float(np.median(ts)), len(ts)
+
+
+def metric_of(wk, args):
+    return {"spmm": ("spmm_effective_hbm_gbs", "GB/s"), "spmv": ("spmv_effective_hbm_gbs", "GB/s"),
+            "mlp": ("sparse_mlp_samples_per_s", "samples/s"), "conv": ("conv_effective_hbm_gbs", "GB/s")}[wk["kind"]]
+
+
+def job_bytes_flops(wk, nnz_total):
+    """Algorithmic bytes and flops of the WHOLE job (all ranks), one step."""
+    k = wk["kind"]
+    if k == "spmm":
+        return spmm_bytes(nnz_total, wk["m"], wk["n"], wk["C"], wk["bias"] is not None), 2.0 * nnz_total * wk["C"]
+    if k == "spmv":
+        return spmv_bytes(nnz_total, wk["m"], wk["n"]), 2.0 * nnz_total
+    if k == "mlp":
+        B = wk["B"]
+        by, fl = 0, 0.0
+        for W in wk["weights"]:
+            z = int(np.count_nonzero(W))
+            by += 8 * z + 8 * W.shape[0] + 4 * B * (W.shape[0] + W.shape[1])
+            fl += 2.0 * z * B
+        return by, fl
+    if k == "conv":
+        z = int(np.count_nonzero(wk["weights"][0]))
+        cols = wk["B"] * wk["H"] * wk["W"]
+        return 4 * cols * 2 * wk["C"] + 8 * z + 8 * wk["C"], 2.0 * z * cols
+    raise SystemExit(k)
+
+
+def to_value(wk, job_bytes, seconds):
+    if wk["kind"] == "mlp":
+        return wk["B"] / seconds
+    return job_bytes / seconds / 1e9
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wk = build_workload(args, 0, 1)
+    nnz_total = int(wk["csr"][0][-1]) if "csr" in wk else 0
+    job_bytes, job_flops = job_bytes_flops(wk, nnz_total)
+    run, frac, kind, sample = cpu_sample_runner(args, wk)
+    med, reps = time_cpu(run, args.steps, warmup=max(1, min(args.warmup, 2)))
+    sec_full = med / frac
+    metric, unit = metric_of(wk, args)
+    value = to_value(wk, job_bytes, sec_full)
+    cores = host_cores()
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": reps,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": sec_full * 1e3, "higher_is_better": True,
+        "scaling": "strong" if wk["kind"] in ("spmm", "spmv") else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": args.workload, "desc": wk["desc"]},
+        "gflops": job_flops / sec_full / 1e9,
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind,
+                         "sample": sample + f"; median of {reps} runs of {med * 1e3:.2f} ms, scaled by 1/{frac:.4f} to the whole job"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import spx_ctypes as sx
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = sx.Lib()
+    lib.spx_set_device(local)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    wk = build_workload(args, rank, world)
+    kind = wk["kind"]
+    flush_buf = None
+    h2d = d2h = 0
+    e2e_step = None
+    ag_step = None
+
+    if kind in ("spmm", "spmv"):
+        rowptr, col, val = wk["csr"]
+        ell = lib.ell_create_csr(wk["rows"], wk["n"], rowptr, col, val)
+        local_nnz = torch.tensor([ell.nnz_total], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(local_nnz)
+        nnz_total = int(local_nnz.item())
+        dB = None if wk["bias"] is None else torch.from_numpy(wk["bias"]).to(dev)
+        if kind == "spmm":
+            C = wk["C"]
+            dX = torch.from_numpy(wk["X"]).to(dev)
+            dY = torch.empty((wk["rows"], C), device=dev, dtype=torch.float32)
+
+            def step():
+                ell.spmm(dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, dY.data_ptr(), C, stream)
+            hX = torch.from_numpy(wk["X"]).pin_memory()
+            hY = torch.empty((wk["rows"], C), dtype=torch.float32).pin_memory()
+            hB = None if wk["bias"] is None else torch.from_numpy(wk["bias"]).pin_memory()
+            h2d = hX.numel() * 4 + (0 if hB is None else hB.numel() * 4)
+            d2h = hY.numel() * 4
+
+            def e2e_step():
+                lib.spx_spmm_host(ell.h, hX.data_ptr(), C, 0 if hB is None else hB.data_ptr(), sx.ACT_NONE, hY.data_ptr())
+            if world > 1:
+                Yfull = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
+                Yslab = Yfull[wk["row0"]:wk["row0"] + wk["rows"]]
+
+                def ag_step():
+                    ell.spmm(dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, Yslab.data_ptr(), C, stream)
+                    dist.all_gather_into_tensor(Yfull, Yslab)
+            working_set = (wk["n"] * C + wk["rows"] * C) * 4 + 8 * ell.nnz_total
+        else:
+            dx = torch.from_numpy(wk["x"]).to(dev)
+            dy = torch.empty(wk["rows"], device=dev, dtype=torch.float32)
+
+            def step():
+                ell.spmv(dx.data_ptr(), 0 if dB is None else dB.data_ptr(), dy.data_ptr(), stream)
+            hx = torch.from_numpy(wk["x"]).pin_memory()
+            hy = torch.empty(wk["rows"], dtype=torch.float32).pin_memory()
+            hB = None if wk["bias"] is None else torch.from_numpy(wk["bias"]).pin_memory()
+            h2d = hx.numel() * 4 + (0 if hB is None else hB.numel() * 4)
+            d2h = hy.numel() * 4
+
+            def e2e_step():
+                lib.spx_spmv_host(ell.h, hx.data_ptr(), 0 if hB is None else hB.data_ptr(), hy.data_ptr())
+            working_set = 8 * ell.nnz_total + 4 * wk["n"]
+        kernel_name = "spmm" if kind == "spmm" else "spmv"
+    elif kind == "mlp":
+        import tempfile
+
+        import onnx_wire
+        import sparseops_backend as sb
+        sb.set_device(local)
+        B = wk["B"]
+        f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+        f.write(onnx_wire.mlp_model(wk["weights"], wk["biases"], wk["acts"], B))
+        f.close()
+        model = sb.SparseOnnxModel(f.name)
+        os.unlink(f.name)
+        nnz_total = 0
+        x_mem = np.ascontiguousarray(wk["x"].T)                  # [features][B]
+        if world > 1 and args.tp:
+            idbuf = [sb.comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(idbuf, src=0)
+            model.shard_rows(rank, world, idbuf[0])
+            Bl, xl = B, x_mem
+            rows_pad = -(-model.out_features // world) * world
+        else:
+            Bl = B // world
+            xl = np.ascontiguousarray(x_mem[:, rank * Bl:(rank + 1) * Bl])
+            rows_pad = model.out_features
+        model.resize_buffers(Bl)
+        dX = torch.from_numpy(xl).to(dev)
+        dY = torch.empty((rows_pad, Bl), device=dev, dtype=torch.float32)
+
+        def step():
+            model.run_device(dX.data_ptr(), Bl, dY.data_ptr(), stream)
+        hX = torch.from_numpy(xl).pin_memory()
+        h2d, d2h = hX.numel() * 4, model.out_features * Bl * 4
+
+        def e2e_step():
+            model.run(hX.numpy().reshape(Bl, -1))
+        working_set = 64 << 20
+        kernel_name = "spmm"
+    elif kind == "conv":
+        B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
+        import sparseops_backend as sb
+        sb.set_device(local)
+        Eh = sb.encode_host(wk["weights"][0].reshape(Cc, -1))
+        ell = lib.ell_create(Eh.Wd, Eh.idx, Eh.nnz, Eh.n)
+        nnz_total = 0
+        Bl = B // world
+        x_pf = np.ascontiguousarray(wk["x_nchw"][rank * Bl:(rank + 1) * Bl].transpose(1, 2, 3, 0))
+        g = sx.conv_geom(Cc, Cc, 3, 3, H, W, pH=1, pW=1)
+        dX = torch.from_numpy(x_pf).to(dev)
+        dB = torch.from_numpy(wk["biases"][0]).to(dev)
+        dY = torch.empty((Cc, H, W, Bl), device=dev, dtype=torch.float32)
+
+        def step():
+            ell.conv2d(g, sx.LAYOUT_PF, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
+        hX = torch.from_numpy(x_pf).pin_memory()
+        hY = torch.empty((Cc, H, W, Bl), dtype=torch.float32).pin_memory()
+        h2d, d2h = hX.numel() * 4, hY.numel() * 4
+
+        def e2e_step():
+            dX.copy_(hX, non_blocking=True)
+            ell.conv2d(g, sx.LAYOUT_PF, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
+            hY.copy_(dY, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        working_set = (dX.numel() + dY.numel()) * 4
+        kernel_name = "conv"
+
+    job_bytes, job_flops = job_bytes_flops(wk, nnz_total)
+    need_flush = working_set < (256 << 20)
+    if need_flush:
+        flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    counted = {"launches": 0}
+
+    def timed(fn, steps, warmup, flush):
+        """Device time of `steps` calls (CUDA events on the launching stream), seconds."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        launches0 = lib.spx_launch_count()
+        if flush:
+            evs = []
+            for _ in range(steps):
+                flush_buf.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                evs.append((e0, e1))
+            barrier()
+            total = sum(a.elapsed_time(b) for a, b in evs) / 1e3
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            barrier()
+            total = e0.elapsed_time(e1) / 1e3
+        counted["launches"] = lib.spx_launch_count() - launches0
+        t = torch.tensor([total], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    warm = max(3, args.warmup)
+    with ClockSampler(local) as clocks:
+        total = timed(step, args.steps, warm, need_flush)
+        launches = counted["launches"]
+    sec = total / args.steps
+    launches_per_step = launches // max(1, args.steps)
+
+    e2e = None
+    if not args.no_e2e and e2e_step is not None:
+        def e2e_wall(steps, warmup):
+            for _ in range(warmup):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                e2e_step()          # synchronous: returns after the device->host copy has landed
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            t = torch.tensor([dt], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item()) / steps
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_sec = e2e_wall(e2e_steps, 2)
+        e2e = {"value": to_value(wk, job_bytes, e2e_sec), "unit": metric_of(wk, args)[1], "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
+               "timing": "host wall clock around synchronous host-buffer calls, max over ranks"}
+
+    ag = None
+    if ag_step is not None:
+        ag_total = timed(ag_step, max(3, min(args.steps, 10)), 2, False)
+        ag_sec = ag_total / max(3, min(args.steps, 10))
+        ag = {"ms_per_step": ag_sec * 1e3, "value": to_value(wk, job_bytes, ag_sec),
+              "note": "SpMM + NCCL all-gather of Y into every rank's full buffer"}
+
+    if rank == 0:
+        metric, unit = metric_of(wk, args)
+        peak, peak_kind = measured_peak()
+        per_gpu_bytes = job_bytes / world if kind != "mlp" else job_bytes
+        achieved = per_gpu_bytes / sec / 1e9
+        line = {
+            "metric": metric, "value": to_value(wk, job_bytes, sec), "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong" if kind in ("spmm", "spmv") else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "desc": wk["desc"],
+                       "l2": "flushed between timed iterations (512 MiB write)" if need_flush else "inputs larger than L2",
+                       "sharding": "rows of E split over ranks, X replicated, Y row-sharded" if kind in ("spmm", "spmv")
+                       else ("row-sharded layers + all-gather" if args.tp else "batch-sharded, no collective")},
+            "gflops": job_flops / sec / 1e9,
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"of {peak_kind}", "kernel": kernel_name,
+                         "algorithmic_bytes_per_launch": per_gpu_bytes / max(1, launches_per_step) if kind != "mlp" else None,
+                         "traffic": recorded_traffic(kernel_name, args.workload)},
+        }
+        if e2e:
+            line["e2e"] = e2e
+        if ag:
+            line["with_allgather"] = ag
+        if not args.no_cpu and world == 1:
+            try:
+                run, frac, ckind, sample = cpu_sample_runner(args, wk)
+                med, reps = time_cpu(run, 5, warmup=1, budget_s=20.0)
+                csec = med / frac
+                line["cpu_baseline"] = {"value": to_value(wk, job_bytes, csec), "unit": unit, "cores": host_cores(), "kind": ckind,
+                                        "sample": sample + f"; median of {reps} runs of {med * 1e3:.2f} ms, scaled by 1/{frac:.4f}",
+                                        "gflops": job_flops / csec / 1e9}
+            except Exception as ex:  # the CPU leg must never take the GPU line down
+                line["cpu_baseline"] = {"value": None, "error": repr(ex)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,164 @@
+/*
+ * spx_b200.h -- C ABI of libspx_b200.so: the CUDA (sm_100a) implementation of the
+ * sparse-ops ELLPACK hot path.  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Conventions
+ *   - Every function returns an int status (SPX_OK == 0).  On failure a thread-local
+ *     message is available from spx_last_error().  No exception crosses this boundary.
+ *   - "device pointer" arguments must point into the memory of the CUDA device that was
+ *     current (spx_set_device) when the spx_ell handle was created.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Kernel
+ *     entry points only enqueue work; they do not synchronise.
+ *   - There is no CPU fallback: without a usable CUDA device every compute entry point
+ *     fails with SPX_ERR_CUDA.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside the
+ * sparse-ops project).
+ */
+#ifndef SPX_B200_H
+#define SPX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPX_OK            0
+#define SPX_ERR_ARG       1   /* bad argument (null pointer, shape mismatch, misuse) */
+#define SPX_ERR_CUDA      2   /* a CUDA runtime call failed */
+#define SPX_ERR_OOM       3   /* device or pinned-host allocation failed */
+#define SPX_ERR_LIMIT     4   /* size beyond what an entry point supports */
+#define SPX_ERR_COMM      5   /* NCCL / communicator failure */
+#define SPX_ERR_TIMEOUT   6   /* a bounded device-side wait gave up */
+
+/* Activation fused into a kernel epilogue.  RELU replaces the FUSE_RELU template flag of
+ * ellpack_matmul_fused (src/ellpack_matmul.cpp:11,68-70); SIGMOID / TANH replace the
+ * separate applySigmoid / applyTanh passes (src/layers/activation.cpp:24-61). */
+#define SPX_ACT_NONE      0
+#define SPX_ACT_RELU      1
+#define SPX_ACT_SIGMOID   2
+#define SPX_ACT_TANH      3
+
+/* Activation tensor layouts of the convolution. */
+#define SPX_LAYOUT_PF     0   /* [C,H,W,B], batch fastest: conv2d_patchmajor_tiled, src/layers/conv_kernels.cpp:342 */
+#define SPX_LAYOUT_NCHW   1   /* [B,C,H,W]: conv2d_tiled_im2col_cmajor, src/layers/conv_kernels.cpp:233 */
+
+/* Elementwise operators of spx_eltwise. */
+#define SPX_OP_RELU       1
+#define SPX_OP_SIGMOID    2
+#define SPX_OP_TANH       3
+#define SPX_OP_ADD        4
+
+/* Device-resident ELLPACK matrix: replaces struct Ellpack (include/ellpack_encoder.hpp:6-23).
+ * Wd / idx live in device memory as row-major slabs whose row pitch is r rounded up to 32
+ * entries (128-byte aligned rows); nnz[m] drives every kernel, padding is never multiplied.
+ * The reference's Xt gather scratch has no device counterpart. */
+typedef struct spx_ell spx_ell;
+
+/* Geometry of one convolution: the numeric fields of ConvAttr (include/sparse_onnx.hpp:64-92).
+ * Begin pads only, as the loader reads them (src/sparse_onnx.cpp:411).
+ * Ho = (H + 2*pH - (dH*(kH-1)+1))/sH + 1, likewise Wo (src/sparse_onnx.cpp:428-429). */
+typedef struct spx_conv_geom {
+    uint32_t Cin, Cout, kH, kW;
+    uint32_t sH, sW, pH, pW, dH, dW;
+    uint32_t H, W, Ho, Wo;
+} spx_conv_geom;
+
+/* ---- library / device ----------------------------------------------------------------- */
+const char* spx_last_error(void);
+int spx_version(void);
+int spx_device_count(int* count);
+int spx_set_device(int device);
+int spx_get_device(int* device);
+int spx_device_sync(void);
+/* Number of kernels this library has launched in this process (all entry points). */
+uint64_t spx_launch_count(void);
+
+/* ---- memory, streams, events (so that host code above this ABI needs no CUDA headers) -- */
+int spx_malloc(void** dptr, size_t bytes);            /* 256-byte aligned device memory */
+int spx_free(void* dptr);
+int spx_host_alloc(void** hptr, size_t bytes);        /* pinned host memory */
+int spx_host_free(void* hptr);
+int spx_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int spx_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int spx_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int spx_memset(void* dst, int value, size_t bytes, void* stream);
+int spx_stream_create(void** stream);
+int spx_stream_destroy(void* stream);
+int spx_stream_sync(void* stream);
+int spx_event_create(void** event);
+int spx_event_destroy(void* event);
+int spx_event_record(void* event, void* stream);
+int spx_event_elapsed_ms(void* start, void* stop, float* ms);   /* synchronises on stop */
+
+/* ---- CUDA graphs (the captured layer loop of SparseOnnxModel::run) ---------------------- */
+int spx_graph_capture_begin(void* stream);
+int spx_graph_capture_end(void* stream, void** graph_exec);
+int spx_graph_launch(void* graph_exec, void* stream);
+int spx_graph_destroy(void* graph_exec);
+
+/* ---- ELLPACK handles ------------------------------------------------------------------- */
+/* Upload host arrays in the reference layout (Wd, idx: m*r row-major; nnz: m).
+ * Replaces the Ellpack constructor + convert_to_ellpack's output (src/ellpack_encoder.cpp:20-41).
+ * Every idx < n and nnz[i] <= r is checked on the host before the upload. */
+int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const uint32_t* idx,
+                   const uint32_t* nnz, spx_ell** out);
+/* Build the device ELLPACK from host CSR (rowptr: m+1 entries; columns ascending per row).
+ * For matrices whose dense form cannot exist; r = the longest row.  The reference only has
+ * the dense route (src/ellpack_encoder.cpp:6). */
+int spx_ell_create_csr(uint32_t m, uint32_t n, const uint64_t* rowptr, const uint32_t* col,
+                       const float* val, spx_ell** out);
+/* Encode a dense row-major m*n device matrix on the device: same result as
+ * convert_to_ellpack (src/ellpack_encoder.cpp:6-44): entries with v != 0.0f, ascending columns. */
+int spx_ell_encode_device(const float* dW, uint32_t m, uint32_t n, void* stream, spx_ell** out);
+int spx_ell_destroy(spx_ell* e);
+int spx_ell_dims(const spx_ell* e, uint32_t* m, uint32_t* n, uint32_t* r, uint64_t* nnz_total);
+/* Copy back in the reference layout (any pointer may be NULL). */
+int spx_ell_download(const spx_ell* e, float* Wd, uint32_t* idx, uint32_t* nnz);
+/* Dense m*n row-major device output: decode_from_ellpack (src/ellpack_encoder.cpp:46-60). */
+int spx_ell_decode_device(const spx_ell* e, float* dW, void* stream);
+
+/* ---- kernels on device-resident operands ------------------------------------------------ */
+/* Y[i,c] = act(bias[i] + sum_j Wd[i,j] * X[idx[i,j], c]), j in storage order, one FMA each.
+ * Replaces ellpack_matmul (include/ellpack_matmul.hpp:23-43) and
+ * ellpack_matmul_fused<USE_MASK,FUSE_RELU> (src/ellpack_matmul.cpp:11-92).
+ * X: n rows of ldx floats (C used), Y: m rows of ldy floats.  bias may be NULL (= 0). */
+int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
+             int act, float* Y, uint64_t ldy, void* stream);
+/* y[i] = bias[i] + sum_j Wd[i,j] * x[idx[i,j]].  Replaces ellpack_matvec
+ * (src/ellpack_matvec.cpp:20-147).  bias may be NULL. */
+int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void* stream);
+/* Sparse convolution by implicit im2col; e is the ELLPACK of the weight flattened to
+ * [Cout x Cin*kH*kW].  Replaces conv2d_patchmajor_tiled / conv2d_tiled_im2col_cmajor /
+ * conv2d_tiled_im2col_fmajor / conv2d_rbm_fmajor_implicit (src/layers/conv_kernels.cpp:66-470). */
+int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
+               const float* bias, int act, float* out, void* stream);
+/* out = op(a[, b]) elementwise; replaces applyRelu/Sigmoid/Tanh (src/layers/activation.cpp:3-62),
+ * relu/sigmoid/tanh_inplace (src/activations.cpp:20-68) and applyAdd (src/layers/add.cpp:9-76).
+ * out may alias a. */
+int spx_eltwise(int op, const float* a, const float* b, float* out, uint64_t count, void* stream);
+
+/* ---- the same calls on HOST buffers (what the reference's Python binding does) ---------- */
+/* X, bias, Y are host arrays; copies in and out go through pinned staging owned by the
+ * handle's device context.  Replaces the ellpack_matmul / ellpack_matvec lambdas of
+ * src/bindings.cpp:91-139.  Synchronous. */
+int spx_spmm_host(const spx_ell* e, const float* X, uint32_t C, const float* bias, int act, float* Y);
+int spx_spmv_host(const spx_ell* e, const float* x, const float* bias, float* y);
+
+/* ---- communicator for the row-sharded paths (one process per GPU, NCCL) ------------------ */
+typedef struct spx_comm spx_comm;
+#define SPX_UNIQUE_ID_BYTES 128
+int spx_comm_unique_id(char id[SPX_UNIQUE_ID_BYTES]);
+int spx_comm_create(int rank, int world, const char id[SPX_UNIQUE_ID_BYTES], spx_comm** out);
+int spx_comm_destroy(spx_comm* c);
+/* In-place all-gather of row slabs: rank g's rows_per_rank*ld floats already sit at
+ * Y + g*rows_per_rank*ld of the full buffer.  (The reference has no multi-device path; this is
+ * the exchange step of row-sharded SpMM, src/ellpack_matmul.cpp:26 being the row loop it splits.) */
+int spx_allgather_rows(spx_comm* c, float* Y, uint64_t rows_per_rank, uint64_t ld, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPX_B200_H */

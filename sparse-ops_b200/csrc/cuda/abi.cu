@@ -1,0 +1,466 @@
+// abi.cu -- the extern "C" surface of libspx_b200.so (declared in include/spx_b200.h):
+// error reporting, device memory / streams / events / graphs, ELLPACK handle life cycle,
+// argument validation in front of every kernel launcher, and the host-buffer entry points
+// that copy operands through pinned staging.
+#include "common.cuh"
+
+#include <dlfcn.h>
+
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+namespace spx {
+
+static thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count(int device)
+{
+    static std::mutex mu;
+    static int cache[64];
+    static bool have[64];
+    if (device < 0 || device >= 64) return 148;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!have[device]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) v = 148;
+        cache[device] = v;
+        have[device] = true;
+    }
+    return cache[device];
+}
+
+int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out)
+{
+    spx_ell* e = new (std::nothrow) spx_ell();
+    if (!e) return fail(SPX_ERR_OOM, "out of host memory");
+    {
+        cudaError_t derr = cudaGetDevice(&e->device);
+        if (derr != cudaSuccess) {
+            delete e;
+            return fail(SPX_ERR_CUDA, "no usable CUDA device: %s", cudaGetErrorString(derr));
+        }
+    }
+    e->m = m; e->n = n; e->r = r;
+    e->pitch = r ? round_up<uint32_t>(r, 32u) : 0u;
+    const size_t slots = (size_t)m * e->pitch;
+    cudaError_t err = cudaSuccess;
+    if (slots) {
+        err = cudaMalloc(&e->Wd, slots * sizeof(float));
+        if (err == cudaSuccess) err = cudaMalloc(&e->idx, slots * sizeof(uint32_t));
+        // padding slots hold Wd = 0.0f, idx = 0 like the reference's (src/ellpack_encoder.cpp:25)
+        if (err == cudaSuccess) err = cudaMemset(e->Wd, 0, slots * sizeof(float));
+        if (err == cudaSuccess) err = cudaMemset(e->idx, 0, slots * sizeof(uint32_t));
+    }
+    if (err == cudaSuccess && m) err = cudaMalloc(&e->nnz, (size_t)m * sizeof(uint32_t));
+    if (err == cudaSuccess && m) err = cudaMemset(e->nnz, 0, (size_t)m * sizeof(uint32_t));
+    if (err != cudaSuccess) {
+        cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz);
+        delete e;
+        return fail(err == cudaErrorMemoryAllocation ? SPX_ERR_OOM : SPX_ERR_CUDA,
+                    "ELLPACK device allocation (%zu slots) failed: %s", slots, cudaGetErrorString(err));
+    }
+    *out = e;
+    return SPX_OK;
+}
+
+// Device scratch owned by a handle for the host-buffer entry points.
+static int ensure_stage(spx_ell* e, size_t bytes)
+{
+    if (e->stage_dev_bytes >= bytes) return SPX_OK;
+    if (e->stage_dev) cudaFree(e->stage_dev);
+    e->stage_dev = nullptr;
+    e->stage_dev_bytes = 0;
+    SPX_CUDA(cudaMalloc(&e->stage_dev, bytes));
+    e->stage_dev_bytes = bytes;
+    return SPX_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+};
+
+}  // namespace spx
+
+using namespace spx;
+
+extern "C" {
+
+const char* spx_last_error(void) { return g_err; }
+int spx_version(void) { return 100; }
+
+int spx_device_count(int* count)
+{
+    if (!count) return fail(SPX_ERR_ARG, "count is null");
+    SPX_CUDA(cudaGetDeviceCount(count));
+    return SPX_OK;
+}
+int spx_set_device(int device) { SPX_CUDA(cudaSetDevice(device)); return SPX_OK; }
+int spx_get_device(int* device)
+{
+    if (!device) return fail(SPX_ERR_ARG, "device is null");
+    SPX_CUDA(cudaGetDevice(device));
+    return SPX_OK;
+}
+int spx_device_sync(void) { SPX_CUDA(cudaDeviceSynchronize()); return SPX_OK; }
+uint64_t spx_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+// ---- memory / streams / events -----------------------------------------------------------
+int spx_malloc(void** dptr, size_t bytes)
+{
+    if (!dptr) return fail(SPX_ERR_ARG, "dptr is null");
+    *dptr = nullptr;
+    if (bytes == 0) return SPX_OK;
+    SPX_CUDA(cudaMalloc(dptr, bytes));
+    return SPX_OK;
+}
+int spx_free(void* dptr) { if (dptr) SPX_CUDA(cudaFree(dptr)); return SPX_OK; }
+int spx_host_alloc(void** hptr, size_t bytes)
+{
+    if (!hptr) return fail(SPX_ERR_ARG, "hptr is null");
+    *hptr = nullptr;
+    if (bytes == 0) return SPX_OK;
+    SPX_CUDA(cudaMallocHost(hptr, bytes));
+    return SPX_OK;
+}
+int spx_host_free(void* hptr) { if (hptr) SPX_CUDA(cudaFreeHost(hptr)); return SPX_OK; }
+int spx_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes) SPX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes) SPX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes) SPX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_memset(void* dst, int value, size_t bytes, void* stream)
+{
+    if (bytes) SPX_CUDA(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_stream_create(void** stream)
+{
+    if (!stream) return fail(SPX_ERR_ARG, "stream is null");
+    cudaStream_t s;
+    SPX_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return SPX_OK;
+}
+int spx_stream_destroy(void* stream) { if (stream) SPX_CUDA(cudaStreamDestroy((cudaStream_t)stream)); return SPX_OK; }
+int spx_stream_sync(void* stream) { SPX_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); return SPX_OK; }
+int spx_event_create(void** event)
+{
+    if (!event) return fail(SPX_ERR_ARG, "event is null");
+    cudaEvent_t ev;
+    SPX_CUDA(cudaEventCreate(&ev));
+    *event = ev;
+    return SPX_OK;
+}
+int spx_event_destroy(void* event) { if (event) SPX_CUDA(cudaEventDestroy((cudaEvent_t)event)); return SPX_OK; }
+int spx_event_record(void* event, void* stream)
+{
+    SPX_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_event_elapsed_ms(void* start, void* stop, float* ms)
+{
+    if (!ms) return fail(SPX_ERR_ARG, "ms is null");
+    SPX_CUDA(cudaEventSynchronize((cudaEvent_t)stop));
+    SPX_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return SPX_OK;
+}
+
+// ---- graphs --------------------------------------------------------------------------------
+int spx_graph_capture_begin(void* stream)
+{
+    if (!stream) return fail(SPX_ERR_ARG, "graph capture needs a non-default stream");
+    SPX_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return SPX_OK;
+}
+int spx_graph_capture_end(void* stream, void** graph_exec)
+{
+    if (!graph_exec) return fail(SPX_ERR_ARG, "graph_exec is null");
+    cudaGraph_t g = nullptr;
+    SPX_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t ge = nullptr;
+    cudaError_t err = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(err));
+    *graph_exec = ge;
+    return SPX_OK;
+}
+int spx_graph_launch(void* graph_exec, void* stream)
+{
+    SPX_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, (cudaStream_t)stream));
+    return SPX_OK;
+}
+int spx_graph_destroy(void* graph_exec)
+{
+    if (graph_exec) SPX_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+    return SPX_OK;
+}
+
+// ---- ELLPACK handles -------------------------------------------------------------------------
+int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const uint32_t* idx,
+                   const uint32_t* nnz, spx_ell** out)
+{
+    if (!out) return fail(SPX_ERR_ARG, "out is null");
+    *out = nullptr;
+    if (m && !nnz) return fail(SPX_ERR_ARG, "nnz is null");
+    if ((size_t)m * r && (!Wd || !idx)) return fail(SPX_ERR_ARG, "Wd / idx is null");
+    // Host-side validation in place of a device-side sanitizer: every stored column id must
+    // be a valid row of X, every count must fit the slab.
+    uint64_t total = 0;
+    uint32_t longest = 0;
+    for (uint32_t i = 0; i < m; ++i) {
+        const uint32_t c = nnz[i];
+        if (c > r) return fail(SPX_ERR_ARG, "nnz[%u] = %u exceeds r = %u", i, c, r);
+        const uint32_t* row = idx + (size_t)i * r;
+        for (uint32_t j = 0; j < c; ++j)
+            if (row[j] >= n) return fail(SPX_ERR_ARG, "idx[%u,%u] = %u is not below n = %u", i, j, row[j], n);
+        total += c;
+        if (c > longest) longest = c;
+    }
+    spx_ell* e = nullptr;
+    int rc = alloc_ell(m, n, r, &e);
+    if (rc != SPX_OK) return rc;
+    e->nnz_total = total;
+    e->max_nnz = longest;
+    cudaError_t err = cudaSuccess;
+    if ((size_t)m * r) {
+        err = cudaMemcpy2D(e->Wd, (size_t)e->pitch * 4, Wd, (size_t)r * 4, (size_t)r * 4, m, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess)
+            err = cudaMemcpy2D(e->idx, (size_t)e->pitch * 4, idx, (size_t)r * 4, (size_t)r * 4, m, cudaMemcpyHostToDevice);
+    }
+    if (err == cudaSuccess && m) err = cudaMemcpy(e->nnz, nnz, (size_t)m * 4, cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) {
+        spx_ell_destroy(e);
+        return fail(SPX_ERR_CUDA, "ELLPACK upload failed: %s", cudaGetErrorString(err));
+    }
+    *out = e;
+    return SPX_OK;
+}
+
+int spx_ell_create_csr(uint32_t m, uint32_t n, const uint64_t* rowptr, const uint32_t* col,
+                       const float* val, spx_ell** out)
+{
+    if (!out) return fail(SPX_ERR_ARG, "out is null");
+    *out = nullptr;
+    if (!rowptr) return fail(SPX_ERR_ARG, "rowptr is null");
+    if (rowptr[0] != 0) return fail(SPX_ERR_ARG, "rowptr[0] must be 0");
+    uint32_t r = 0;
+    for (uint32_t i = 0; i < m; ++i) {
+        if (rowptr[i + 1] < rowptr[i]) return fail(SPX_ERR_ARG, "rowptr is not non-decreasing at row %u", i);
+        const uint64_t c = rowptr[i + 1] - rowptr[i];
+        if (c > n) return fail(SPX_ERR_ARG, "row %u has more entries than columns", i);
+        if (c > r) r = (uint32_t)c;
+    }
+    const uint64_t total = rowptr[m];
+    if (total && (!col || !val)) return fail(SPX_ERR_ARG, "col / val is null");
+    for (uint32_t i = 0; i < m; ++i)
+        for (uint64_t j = rowptr[i]; j < rowptr[i + 1]; ++j) {
+            if (col[j] >= n) return fail(SPX_ERR_ARG, "col[%llu] = %u is not below n = %u", (unsigned long long)j, col[j], n);
+            if (j > rowptr[i] && col[j] <= col[j - 1])
+                return fail(SPX_ERR_ARG, "columns of row %u are not strictly ascending", i);
+        }
+    spx_ell* e = nullptr;
+    int rc = alloc_ell(m, n, r, &e);
+    if (rc != SPX_OK) return rc;
+    e->nnz_total = total;
+    e->max_nnz = r;
+    if (m) {
+        uint64_t* d_rowptr = nullptr; uint32_t* d_col = nullptr; float* d_val = nullptr;
+        cudaError_t err = cudaMalloc(&d_rowptr, (size_t)(m + 1) * 8);
+        if (err == cudaSuccess && total) err = cudaMalloc(&d_col, total * 4);
+        if (err == cudaSuccess && total) err = cudaMalloc(&d_val, total * 4);
+        if (err == cudaSuccess) err = cudaMemcpy(d_rowptr, rowptr, (size_t)(m + 1) * 8, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess && total) err = cudaMemcpy(d_col, col, total * 4, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess && total) err = cudaMemcpy(d_val, val, total * 4, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) {
+            rc = csr_to_ell_device(e, d_rowptr, d_col, d_val, nullptr);
+            if (rc == SPX_OK) err = cudaDeviceSynchronize();
+        }
+        cudaFree(d_rowptr); cudaFree(d_col); cudaFree(d_val);
+        if (err != cudaSuccess || rc != SPX_OK) {
+            spx_ell_destroy(e);
+            return rc != SPX_OK ? rc : fail(err == cudaErrorMemoryAllocation ? SPX_ERR_OOM : SPX_ERR_CUDA,
+                                            "CSR upload failed: %s", cudaGetErrorString(err));
+        }
+    }
+    *out = e;
+    return SPX_OK;
+}
+
+int spx_ell_encode_device(const float* dW, uint32_t m, uint32_t n, void* stream, spx_ell** out)
+{
+    if (!out) return fail(SPX_ERR_ARG, "out is null");
+    *out = nullptr;
+    if ((size_t)m * n && !dW) return fail(SPX_ERR_ARG, "dW is null");
+    return encode_device(dW, m, n, (cudaStream_t)stream, out);
+}
+
+int spx_ell_destroy(spx_ell* e)
+{
+    if (!e) return SPX_OK;
+    DeviceGuard g(e->device);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->taps); cudaFree(e->stage_dev);
+    delete e;
+    return SPX_OK;
+}
+
+int spx_ell_dims(const spx_ell* e, uint32_t* m, uint32_t* n, uint32_t* r, uint64_t* nnz_total)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (m) *m = e->m;
+    if (n) *n = e->n;
+    if (r) *r = e->r;
+    if (nnz_total) *nnz_total = e->nnz_total;
+    return SPX_OK;
+}
+
+int spx_ell_download(const spx_ell* e, float* Wd, uint32_t* idx, uint32_t* nnz)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    DeviceGuard g(e->device);
+    const size_t rb = (size_t)e->r * 4;
+    if ((size_t)e->m * e->r) {
+        if (Wd) SPX_CUDA(cudaMemcpy2D(Wd, rb, e->Wd, (size_t)e->pitch * 4, rb, e->m, cudaMemcpyDeviceToHost));
+        if (idx) SPX_CUDA(cudaMemcpy2D(idx, rb, e->idx, (size_t)e->pitch * 4, rb, e->m, cudaMemcpyDeviceToHost));
+    }
+    if (nnz && e->m) SPX_CUDA(cudaMemcpy(nnz, e->nnz, (size_t)e->m * 4, cudaMemcpyDeviceToHost));
+    return SPX_OK;
+}
+
+int spx_ell_decode_device(const spx_ell* e, float* dW, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if ((size_t)e->m * e->n && !dW) return fail(SPX_ERR_ARG, "dW is null");
+    return decode_device(e, dW, (cudaStream_t)stream);
+}
+
+// ---- kernels ---------------------------------------------------------------------------------
+int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
+             int act, float* Y, uint64_t ldy, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (e->m == 0 || C == 0) return SPX_OK;
+    if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
+    if (!Y) return fail(SPX_ERR_ARG, "Y is null");
+    if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    return launch_spmm(e, X, C, ldx, bias, act, Y, ldy, (cudaStream_t)stream);
+}
+
+int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (e->m == 0) return SPX_OK;
+    if (!y) return fail(SPX_ERR_ARG, "y is null");
+    if (!x && e->nnz_total) return fail(SPX_ERR_ARG, "x is null");
+    return launch_spmv(e, x, bias, y, (cudaStream_t)stream);
+}
+
+int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
+               const float* bias, int act, float* out, void* stream)
+{
+    if (!e || !g) return fail(SPX_ERR_ARG, "handle / geometry is null");
+    if (layout != SPX_LAYOUT_PF && layout != SPX_LAYOUT_NCHW) return fail(SPX_ERR_ARG, "unknown layout %d", layout);
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (g->sH == 0 || g->sW == 0 || g->dH == 0 || g->dW == 0 || g->kH == 0 || g->kW == 0)
+        return fail(SPX_ERR_ARG, "stride, dilation and kernel extent must be positive");
+    if (e->m != g->Cout) return fail(SPX_ERR_ARG, "ELLPACK rows (%u) != Cout (%u)", e->m, g->Cout);
+    if ((uint64_t)g->Cin * g->kH * g->kW != e->n)
+        return fail(SPX_ERR_ARG, "ELLPACK columns (%u) != Cin*kH*kW", e->n);
+    const uint32_t eh = g->dH * (g->kH - 1) + 1, ew = g->dW * (g->kW - 1) + 1;
+    if (g->H + 2 * g->pH < eh || g->W + 2 * g->pW < ew) return fail(SPX_ERR_ARG, "kernel larger than padded input");
+    if (g->Ho != (g->H + 2 * g->pH - eh) / g->sH + 1 || g->Wo != (g->W + 2 * g->pW - ew) / g->sW + 1)
+        return fail(SPX_ERR_ARG, "Ho / Wo inconsistent with the geometry");
+    if (B == 0 || e->m == 0) return SPX_OK;
+    if (!in || !out) return fail(SPX_ERR_ARG, "in / out is null");
+    return launch_conv2d(const_cast<spx_ell*>(e), g, layout, in, B, bias, act, out, (cudaStream_t)stream);
+}
+
+int spx_eltwise(int op, const float* a, const float* b, float* out, uint64_t count, void* stream)
+{
+    if (op < SPX_OP_RELU || op > SPX_OP_ADD) return fail(SPX_ERR_ARG, "unknown elementwise op %d", op);
+    if (count == 0) return SPX_OK;
+    if (!a || !out || (op == SPX_OP_ADD && !b)) return fail(SPX_ERR_ARG, "null operand");
+    return launch_eltwise(op, a, b, out, count, (cudaStream_t)stream);
+}
+
+// ---- host-buffer entry points ----------------------------------------------------------------
+// Pageable host buffers are copied by the driver through its own pinned bounce buffers; callers
+// that pass pinned memory (spx_host_alloc) get direct DMA.  Layout of the staging block:
+// [X | bias | Y], each part 256-byte aligned.
+int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bias, int act, float* Y)
+{
+    spx_ell* e = const_cast<spx_ell*>(ce);
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (e->m == 0 || C == 0) return SPX_OK;
+    if (!Y || (!X && e->n)) return fail(SPX_ERR_ARG, "X / Y is null");
+    DeviceGuard g(e->device);
+    const size_t xb = round_up<size_t>((size_t)e->n * C * 4, 256);
+    const size_t bb = round_up<size_t>((size_t)e->m * 4, 256);
+    const size_t yb = round_up<size_t>((size_t)e->m * C * 4, 256);
+    int rc = ensure_stage(e, xb + bb + yb);
+    if (rc != SPX_OK) return rc;
+    char* base = static_cast<char*>(e->stage_dev);
+    float* dX = reinterpret_cast<float*>(base);
+    float* dB = reinterpret_cast<float*>(base + xb);
+    float* dY = reinterpret_cast<float*>(base + xb + bb);
+    if (e->n) SPX_CUDA(cudaMemcpyAsync(dX, X, (size_t)e->n * C * 4, cudaMemcpyHostToDevice, nullptr));
+    if (bias) SPX_CUDA(cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, nullptr));
+    rc = spx_spmm(e, dX, C, C, bias ? dB : nullptr, act, dY, C, nullptr);
+    if (rc != SPX_OK) return rc;
+    SPX_CUDA(cudaMemcpyAsync(Y, dY, (size_t)e->m * C * 4, cudaMemcpyDeviceToHost, nullptr));
+    SPX_CUDA(cudaStreamSynchronize(nullptr));
+    return SPX_OK;
+}
+
+int spx_spmv_host(const spx_ell* ce, const float* x, const float* bias, float* y)
+{
+    spx_ell* e = const_cast<spx_ell*>(ce);
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (e->m == 0) return SPX_OK;
+    if (!y || (!x && e->n)) return fail(SPX_ERR_ARG, "x / y is null");
+    DeviceGuard g(e->device);
+    const size_t xb = round_up<size_t>((size_t)e->n * 4, 256);
+    const size_t bb = round_up<size_t>((size_t)e->m * 4, 256);
+    int rc = ensure_stage(e, xb + 2 * bb);
+    if (rc != SPX_OK) return rc;
+    char* base = static_cast<char*>(e->stage_dev);
+    float* dx = reinterpret_cast<float*>(base);
+    float* dB = reinterpret_cast<float*>(base + xb);
+    float* dy = reinterpret_cast<float*>(base + xb + bb);
+    if (e->n) SPX_CUDA(cudaMemcpyAsync(dx, x, (size_t)e->n * 4, cudaMemcpyHostToDevice, nullptr));
+    if (bias) SPX_CUDA(cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, nullptr));
+    rc = spx_spmv(e, dx, bias ? dB : nullptr, dy, nullptr);
+    if (rc != SPX_OK) return rc;
+    SPX_CUDA(cudaMemcpyAsync(y, dy, (size_t)e->m * 4, cudaMemcpyDeviceToHost, nullptr));
+    SPX_CUDA(cudaStreamSynchronize(nullptr));
+    return SPX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,88 @@
+// common.cuh -- shared declarations of the CUDA side of libspx_b200.so (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "spx_b200.h"
+
+// Device-resident ELLPACK (see include/spx_b200.h).  Row i occupies entries
+// [i*pitch, i*pitch + nnz[i]) of Wd / idx; pitch is a multiple of 32 entries so that
+// every row starts on a 128-byte boundary and float4 / uint4 loads are aligned.
+struct spx_ell {
+    int device = 0;
+    uint32_t m = 0, n = 0, r = 0;
+    uint32_t pitch = 0;          // row pitch in entries (0 when r == 0)
+    uint64_t nnz_total = 0;
+    uint32_t max_nnz = 0;        // longest row actually stored (<= r)
+    float* Wd = nullptr;         // m * pitch floats
+    uint32_t* idx = nullptr;     // m * pitch column ids
+    uint32_t* nnz = nullptr;     // m counts
+    // Lazily built, cached conv tap table: idx decoded to packed (cin, kh, kw) for one
+    // kernel shape (conv.cu); keyed by (kH, kW).
+    uint32_t* taps = nullptr;
+    uint32_t taps_kH = 0, taps_kW = 0;
+    // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
+    void* stage_dev = nullptr;
+    size_t stage_dev_bytes = 0;
+};
+
+namespace spx {
+
+int fail(int code, const char* fmt, ...);
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int sm_count(int device);
+
+// Rounds up to a multiple of `to`.
+template <class T> __host__ __device__ inline T round_up(T v, T to) { return (v + to - 1) / to * to; }
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    // Precise expf / tanhf: the library is built without fast-math so that sigmoid and tanh
+    // stay within a few ulp of the C library results of the reference.
+    switch (act) {
+    case SPX_ACT_RELU:    return v > 0.0f ? v : 0.0f;
+    case SPX_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+    case SPX_ACT_TANH:    return tanhf(v);
+    default:              return v;
+    }
+}
+
+}  // namespace spx
+
+#define SPX_CUDA(call)                                                                     \
+    do {                                                                                   \
+        cudaError_t _e = (call);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return spx::fail(_e == cudaErrorMemoryAllocation ? SPX_ERR_OOM : SPX_ERR_CUDA, \
+                             "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e),       \
+                             __FILE__, __LINE__);                                          \
+    } while (0)
+
+#define SPX_LAUNCH_CHECK(name)                                                             \
+    do {                                                                                   \
+        cudaError_t _e = cudaGetLastError();                                               \
+        if (_e != cudaSuccess)                                                             \
+            return spx::fail(SPX_ERR_CUDA, "launch of %s failed: %s", name,                \
+                             cudaGetErrorString(_e));                                      \
+        spx::count_launch();                                                               \
+    } while (0)
+
+// Kernel launchers implemented in the individual .cu files.
+namespace spx {
+int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
+                int act, float* Y, uint64_t ldy, cudaStream_t s);
+int launch_spmv(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
+int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
+                  const float* bias, int act, float* out, cudaStream_t s);
+int launch_eltwise(int op, const float* a, const float* b, float* out, uint64_t count, cudaStream_t s);
+int encode_device(const float* dW, uint32_t m, uint32_t n, cudaStream_t s, spx_ell** out);
+int decode_device(const spx_ell* e, float* dW, cudaStream_t s);
+int csr_to_ell_device(spx_ell* e, const uint64_t* d_rowptr, const uint32_t* d_col, const float* d_val,
+                      cudaStream_t s);
+int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out);
+}  // namespace spx

@@ -1,0 +1,94 @@
+// sparse_onnx.hpp -- SparseOnnxModel: ONNX-driven sparse inference whose layer loop runs on the
+// GPU.  Interface of the reference class (include/sparse_onnx.hpp:139-163): construct from a
+// path, run(input, B, output), output_shape(); plus resize_buffers(B), which the reference's
+// README documents (README.md:144-148).
+//
+// Load time (constructor) follows the reference planner (src/sparse_onnx.cpp:82-636): Gemm /
+// MatMul / Conv weights are ELLPACK-encoded once and kept device-resident, biases are packed
+// into one device array, MatMul/Conv + Relu pairs are fused (:573-620; Sigmoid and Tanh are
+// fused into the producing kernel's epilogue as well -- same values, one pass less).
+//
+// Memory contract of run(), identical to the reference (src/model_run.cpp, src/layers/matmul.cpp:
+// activations are feature-major): the input bytes are read as [in_features x B] for dense
+// models or [Cin, H, W, B] for convolutional ones, B fastest; the output bytes are [M x B] /
+// [Cout, Ho, Wo, B], regardless of the labelled ONNX shape.
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "ellpack.hpp"
+
+namespace spx {
+
+enum class LayerOp { MatMul, Relu, Sigmoid, Tanh, Add, Conv };
+
+struct Layer {
+    LayerOp op;
+    std::unique_ptr<Ellpack> E;        ///< full matrix, host arrays (+ device copy when unsharded)
+    std::unique_ptr<Ellpack> shard;    ///< this rank's rows when row-sharded
+    std::vector<float> bias;           ///< empty = no bias
+    size_t bias_offset = 0;            ///< into the packed device bias array
+    int act = SPX_ACT_NONE;            ///< activation fused into the epilogue
+    spx_conv_geom geom{};              ///< Conv only
+    std::vector<std::string> inputs, outputs;
+    uint64_t out_features = 0;         ///< output elements per batch column
+};
+
+class SparseOnnxModel {
+public:
+    /// upload_weights = false only parses and plans (no CUDA call is made): for inspecting the
+    /// plan on a machine without a GPU; such a model cannot run.
+    explicit SparseOnnxModel(const std::string& onnx_path, bool upload_weights = true);
+    ~SparseOnnxModel();
+    SparseOnnxModel(const SparseOnnxModel&) = delete;
+    SparseOnnxModel& operator=(const SparseOnnxModel&) = delete;
+
+    /// Host buffers in, host buffers out (see the memory contract above).  Re-plans the device
+    /// buffers when B differs from the current batch.
+    void run(const float* input, uint32_t B, float* output) const;
+    /// Device buffers in and out; launches the layer loop on `stream` without synchronising.
+    void run_device(const float* d_input, uint32_t B, float* d_output, void* stream) const;
+    /// Output dims as labelled in the ONNX graph (static shape recorded at load).
+    std::vector<size_t> output_shape() const;
+    /// (Re)allocate the activation buffers for batch B and capture the layer loop as a CUDA graph.
+    void resize_buffers(uint32_t B);
+    /// Tensor-parallel mode: every MatMul / Conv keeps only rows [rank*ceil(m/world), ...) on this
+    /// process's GPU and each layer ends with an in-place NCCL all-gather of the row slabs.
+    /// unique_id: SPX_UNIQUE_ID_BYTES bytes from spx_comm_unique_id, identical on all ranks.
+    void shard_rows(int rank, int world, const char* unique_id);
+
+    uint32_t batch() const { return batch_dim_; }
+    uint32_t in_features() const { return in_features_; }
+    uint64_t out_features() const { return out_features_; }
+    size_t num_layers() const { return layers_.size(); }
+    const Layer& layer(size_t i) const { return layers_[i]; }
+    /// Algorithmic work of one forward pass at batch B: 2 * nnz * columns summed over layers.
+    double flops_per_run(uint32_t B) const;
+
+private:
+    struct Exec;                                   // device buffers, stream, graph (mutable state)
+    void build_exec(uint32_t B) const;
+    void launch_layers(const float* d_in, float* d_out, uint32_t B, void* stream) const;
+
+    std::vector<Layer> layers_;
+    uint32_t batch_dim_ = 1;
+    uint32_t in_features_ = 0;
+    uint64_t out_features_ = 0;
+    std::vector<int> input_shape_;
+    std::unordered_map<std::string, std::vector<int>> shape_map_;
+    std::unordered_map<std::string, std::string> name_alias_;
+    std::string input_name_, output_name_;
+    int rank_ = 0, world_ = 1;
+    spx_comm* comm_ = nullptr;
+    mutable std::unique_ptr<Exec> exec_;
+};
+
+}  // namespace spx
+
+#ifndef SPX_NO_GLOBAL_NAMES
+using spx::SparseOnnxModel;
+#endif

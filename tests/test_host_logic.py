@@ -1,0 +1,166 @@
+"""CPU: host-side logic above the C ABI -- encoder, ONNX wire reader + planner, RBM plan,
+workload generators -- against the golden vectors of the reference."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from conftest import assert_bit_equal
+
+
+@pytest.mark.parametrize("name", ["enc_hand", "enc_special", "enc_zero", "enc_rand"])
+def test_host_encoder_bit_exact(backend, golden, name):
+    E = backend.encode_host(golden[name + "_W"])
+    assert (E.m, E.n) == golden[name + "_W"].shape
+    assert E.r == golden[name + "_Wd_ref"].shape[1]
+    assert_bit_equal(E.Wd, golden[name + "_Wd_ref"], "Wd")
+    assert np.array_equal(E.idx, golden[name + "_idx_ref"])
+    assert np.array_equal(E.nnz, golden[name + "_nnz_ref"])
+    assert_bit_equal(backend.decode_from_ellpack(E), golden[name + "_decoded_ref"], "decode")
+    assert not E.on_device
+
+
+def test_host_encoder_accepts_float64_and_fortran_input(backend, golden):
+    W = golden["enc_rand_W"]
+    for variant in (W.astype(np.float64), np.asfortranarray(W)):
+        E = backend.encode_host(variant)
+        assert np.array_equal(E.idx, golden["enc_rand_idx_ref"])
+    with pytest.raises(RuntimeError):
+        backend.encode_host(np.zeros(5, np.float32))
+
+
+def test_large_encode_uses_threads_and_matches_numpy(backend):
+    rng = np.random.default_rng(3)
+    W = rng.standard_normal((1500, 1200)).astype(np.float32)
+    W[rng.random(W.shape) >= 0.1] = 0
+    E = backend.encode_host(W)
+    assert E.r == np.count_nonzero(W, axis=1).max()
+    assert np.array_equal(backend.decode_from_ellpack(E), W)
+
+
+def _write(blob):
+    f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+    f.write(blob)
+    f.close()
+    return f.name
+
+
+def test_planner_mlp(backend, golden):
+    path = _write(golden["mlp_onnx"].tobytes())
+    try:
+        m = backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    assert m.output_shape() == golden["mlp_shape_ref"].tolist()
+    assert (m.batch, m.in_features, m.out_features) == (16, 40, 10)
+    L = m.layer_summary()
+    # Gemm+Relu, Gemm+Tanh, Gemm+Sigmoid collapse to three fused MatMul layers
+    assert [l["op"] for l in L] == ["MatMul"] * 3
+    assert [l["act"] for l in L] == [1, 3, 2]
+    assert all(l["bias"] for l in L)
+
+
+def test_planner_gemm_matmul_orientation(backend):
+    import onnx_wire as ow
+    rng = np.random.default_rng(5)
+    W = rng.standard_normal((6, 4)).astype(np.float32)      # (M=6 out, N=4 in)
+    cases = {
+        "gemm_transB1": ow.node("Gemm", ["input", "W"], ["y"], [ow.attr_int("transB", 1)]),
+        "gemm_default": ow.node("Gemm", ["input", "W"], ["y"]),               # missing transB means 1
+        "gemm_transB0": ow.node("Gemm", ["input", "Wt"], ["y"], [ow.attr_int("transB", 0)]),
+        "matmul": ow.node("MatMul", ["input", "Wt"], ["y"]),
+    }
+    for name, nd in cases.items():
+        inits = [ow.tensor("W", W), ow.tensor("Wt", W.T.copy(), packed_float_data=True)]
+        path = _write(ow.model([nd], inits, ("input", (2, 4)), ("y", (2, 6))))
+        try:
+            m = backend.SparseOnnxModel(path, upload_weights=False)
+        finally:
+            os.unlink(path)
+        l = m.layer_summary()[0]
+        assert (l["m"], l["n"]) == (6, 4), name
+        assert l["nnz"] == 24
+
+
+def test_planner_conv_and_errors(backend, golden):
+    path = _write(golden["cnn_onnx"].tobytes())
+    try:
+        m = backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    assert m.output_shape() == golden["cnn_shape_ref"].tolist()
+    L = m.layer_summary()
+    assert [l["op"] for l in L] == ["Conv", "Conv"] and [l["act"] for l in L] == [1, 1]
+    assert L[0]["n"] == 6 * 9
+
+    import onnx_wire as ow
+    with pytest.raises(RuntimeError, match="Failed to open/parse ONNX file"):
+        backend.SparseOnnxModel("/nonexistent/model.onnx", upload_weights=False)
+    bad = ow.model([ow.node("Softmax", ["input"], ["y"])], [], ("input", (2, 4)), ("y", (2, 4)))
+    path = _write(bad)
+    try:
+        with pytest.raises(RuntimeError, match="Unsupported ONNX op: Softmax"):
+            backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    w = np.ones((4, 2, 3, 3), np.float32)
+    grouped = ow.model([ow.node("Conv", ["input", "W"], ["y"], [ow.attr_int("group", 2)])], [ow.tensor("W", w)],
+                       ("input", (1, 4, 5, 5)), ("y", (1, 4, 3, 3)))
+    path = _write(grouped)
+    try:
+        with pytest.raises(RuntimeError):
+            backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+
+
+def test_identity_alias_and_unfusable_activation(backend):
+    import onnx_wire as ow
+    W = np.eye(3, dtype=np.float32)
+    nodes = [ow.node("Gemm", ["input", "W"], ["a"]), ow.node("Identity", ["a"], ["b"]),
+             ow.node("Relu", ["b"], ["c"]), ow.node("Add", ["c", "b"], ["d"])]
+    path = _write(ow.model(nodes, [ow.tensor("W", W)], ("input", (2, 3)), ("d", (2, 3))))
+    try:
+        m = backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    L = m.layer_summary()
+    # the Gemm output feeds both Relu and Add, so the Relu must stay a separate layer
+    assert [l["op"] for l in L] == ["MatMul", "Relu", "Add"]
+    assert L[0]["act"] == 0 and L[2]["inputs"] == ["c", "a"]
+
+
+def test_rbm_plan_matches_reference(backend, golden):
+    E = backend.encode_host(golden["conv_a_weight"].reshape(16, -1))
+    blocks = backend.build_rbm_from_ellpack(E, golden["conv_a_bias"], 8)
+    assert [b["M0"] for b in blocks] == golden["rbm_M0"].tolist()
+    assert [b["Ct"] for b in blocks] == golden["rbm_Ct"].tolist()
+    assert [len(b["krel"]) for b in blocks] == golden["rbm_krel_len"].tolist()
+    cat = lambda k: np.concatenate([b[k] for b in blocks])
+    assert np.array_equal(cat("krel"), golden["rbm_krel_ref"])
+    assert np.array_equal(cat("colptr"), golden["rbm_colptr_ref"])
+    assert np.array_equal(cat("rows"), golden["rbm_rows_ref"])
+    assert_bit_equal(cat("w"), golden["rbm_w_ref"], "pair weights")
+    assert_bit_equal(cat("bias"), golden["rbm_bias_ref"], "bias")
+
+
+def test_workload_generators_are_seeded_and_shardable():
+    import workloads as wl
+    a, b = wl.cfg1(0.02), wl.cfg1(0.02)
+    assert np.array_equal(a["W"], b["W"]) and np.array_equal(a["X"], b["X"])
+    # a rank's row range of config 5 reproduces the rows of the whole matrix
+    rp, col, val = wl.cfg5_rows(0, 8192, n=4096, kmax=256, mean=16, block_rows=4096)
+    rp2, col2, val2 = wl.cfg5_rows(4096, 4096, n=4096, kmax=256, mean=16, block_rows=4096)
+    s = int(rp[4096])
+    assert np.array_equal(col[s:], col2) and np.array_equal(val[s:], val2)
+    nnz = np.diff(rp)
+    assert nnz.max() == 256 and 8 < nnz.mean() < 24
+    # strictly ascending columns inside every row
+    d = np.diff(col.astype(np.int64))
+    row_starts = rp[1:-1].astype(np.int64)
+    mask = np.ones(len(d), bool)
+    mask[row_starts[(row_starts > 0) & (row_starts < len(col))] - 1] = False
+    assert (d[mask] > 0).all()
+    Wd, idx, n3 = wl.csr_to_ell(8192, rp, col, val)
+    assert Wd.shape == (8192, 256) and np.array_equal(n3, nnz.astype(np.uint32))

@@ -1,0 +1,174 @@
+"""GPU tests of the drop-in Python module `sparseops_backend`.  The first three tests restate the
+reference's own unit tests (tests/unit/test_ellpack_encoder.py, test_matvec.py, test_matmul.py: same
+shapes, same atol=1e-5 against dense numpy); the rest check the model loop against the golden
+vectors of the reference binary and the extensions (resize_buffers, device pointers, sharding)."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_bit_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def generate_sparse_matrix(M, K, sparsity=0.3, seed=0):
+    dense = np.random.default_rng([M, K, seed]).random((M, K)).astype(np.float32)
+    dense[dense < sparsity] = 0
+    return dense
+
+
+def test_encoder_unit_cases(backend, cuda):
+    W = generate_sparse_matrix(64, 64)
+    E = backend.convert_to_ellpack(W)
+    assert np.allclose(W, backend.decode_from_ellpack(E), atol=1e-5)
+    assert (E.m, E.n) == (64, 64) and E.r == np.max(np.count_nonzero(W, axis=1)) and E.on_device
+    Z = backend.convert_to_ellpack(np.zeros((32, 32), dtype=np.float32))
+    assert (Z.m, Z.n, Z.r) == (32, 32, 0)
+    hand = np.array([[1, 0, 0, 2], [0, 3, 0, 0], [0, 0, 4, 0], [0, 0, 0, 5]], dtype=np.float32)
+    H = backend.convert_to_ellpack(hand)
+    assert H.Wd.shape == (4, 2) and H.Wd[0, 1] == 2.0 and H.Wd[1, 1] == 0.0
+    assert H.idx.tolist() == [[0, 3], [1, 0], [2, 0], [3, 0]]
+    N = backend.convert_to_ellpack(generate_sparse_matrix(64, 32))
+    assert (N.m, N.n) == (64, 32) and backend.decode_from_ellpack(N).shape == (64, 32)
+
+
+MATVEC = [(16, 32, 0.3), (64, 128, 0.5), (128, 256, 0.7), (256, 512, 0.9), (1, 1, 0.0), (1, 1000, 0.1), (1000, 1, 0.1),
+          (0, 0, 0.0), (32, 32, 1.0), (10, 10, 0.0), (10, 10, 0.5), (10, 10, 0.9), (20, 20, 0.2), (100, 100, 0.2),
+          (1000, 1000, 0.1), (500, 500, 0.05), (2000, 2000, 0.3), (3000, 3000, 0.4)]
+
+
+@pytest.mark.parametrize("M,K,sparsity", MATVEC)
+def test_matvec_unit_cases(backend, cuda, M, K, sparsity):
+    W = generate_sparse_matrix(M, K, sparsity)
+    E = backend.convert_to_ellpack(W)
+    x = np.random.default_rng(1).random(K).astype(np.float32)
+    bias = np.random.default_rng(2).random(M).astype(np.float32)
+    y = backend.ellpack_matvec(E, x, bias)
+    assert y.shape == (M,)
+    # dense fp32 numpy sums K terms in a different order: its own rounding error grows with K
+    assert np.allclose(y, W @ x + bias, atol=1e-5 * max(1.0, K / 100))
+    y64 = W.astype(np.float64) @ x + bias
+    assert (np.abs(y - y64) <= 1e-5 * (np.abs(W) @ np.abs(x) + np.abs(bias)) + 1e-12).all()
+
+
+MATMUL = [(16, 32, 1, 0.3), (16, 32, 10, 0.3), (16, 32, 100, 0.3), (64, 128, 10, 0.5), (128, 256, 20, 0.7),
+          (256, 512, 10, 0.9), (1, 1, 1, 0.0), (1, 1000, 1, 0.1), (1000, 1, 1, 0.1), (0, 0, 0, 0.0), (32, 32, 1, 1.0),
+          (10, 10, 1, 0.0), (10, 10, 10, 0.5), (10, 10, 10, 0.9), (20, 20, 10, 0.2), (100, 100, 10, 0.2),
+          (1000, 1000, 10, 0.1), (500, 500, 10, 0.05), (2000, 2000, 10, 0.3), (3000, 3000, 10, 0.4)]
+
+
+@pytest.mark.parametrize("M,K,C,sparsity", MATMUL)
+def test_matmul_unit_cases(backend, cuda, M, K, C, sparsity):
+    W = generate_sparse_matrix(M, K, sparsity)
+    E = backend.convert_to_ellpack(W)
+    X = np.random.default_rng(1).random((K, C)).astype(np.float32)
+    bias = np.random.default_rng(2).random(M).astype(np.float32)
+    Y = backend.ellpack_matmul(E, X, bias)
+    assert Y.shape == (M, C)
+    Y64 = W.astype(np.float64) @ X + bias[:, None]
+    assert (np.abs(Y - Y64) <= 1e-5 * (np.abs(W) @ np.abs(X) + np.abs(bias)[:, None]) + 1e-12).all()
+
+
+def test_binding_errors_and_extras(backend, cuda):
+    E = backend.convert_to_ellpack(generate_sparse_matrix(8, 6))
+    with pytest.raises(RuntimeError, match="X must be 2D"):
+        backend.ellpack_matmul(E, np.ones(6, np.float32), np.ones(8, np.float32))
+    with pytest.raises(RuntimeError, match="Input row count must equal E.n"):
+        backend.ellpack_matmul(E, np.ones((5, 2), np.float32), np.ones(8, np.float32))
+    with pytest.raises(RuntimeError, match="Bias length must equal E.m"):
+        backend.ellpack_matmul(E, np.ones((6, 2), np.float32), np.ones(7, np.float32))
+    x = np.arange(6, dtype=np.float32)
+    y0 = backend.ellpack_matvec(E, x, None)                 # bias=None means no bias
+    assert np.allclose(y0, backend.decode_from_ellpack(E) @ x, atol=1e-5)
+    assert np.array_equal(E.Xt, x[E.idx])                   # what the reference leaves in Xt
+    import cpp_backend
+    assert np.array_equal(cpp_backend.matvec(E, x, np.zeros(8, np.float32)), y0)
+    # float64 / Fortran-ordered inputs are force-cast like the reference does
+    Y = backend.ellpack_matmul(E, np.asfortranarray(np.ones((6, 3))), np.zeros(8))
+    assert Y.dtype == np.float32 and Y.shape == (8, 3)
+
+
+def test_device_pointer_calls_and_row_shards(backend, orc, cuda):
+    rng = np.random.default_rng(9)
+    W = generate_sparse_matrix(100, 64, 0.8)
+    X = rng.uniform(-1, 1, (64, 32)).astype(np.float32)
+    b = rng.standard_normal(100).astype(np.float32)
+    E = backend.convert_to_ellpack(W)
+    want = orc.spmm(orc.encode(W), X, b)
+    dX, dB = torch.from_numpy(X).to(cuda), torch.from_numpy(b).to(cuda)
+    dY = torch.empty((100, 32), device=cuda)
+    backend.ellpack_matmul_device(E, dX.data_ptr(), 32, 32, dB.data_ptr(), 0, dY.data_ptr(), 32)
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), want, "device spmm")
+    # three row shards reproduce the unsharded result bit for bit
+    parts = [backend.ellpack_matmul(E.shard_rows(g, 3), X, b[g * 34:(g + 1) * 34]) for g in range(3)]
+    assert [p.shape[0] for p in parts] == [34, 34, 32]
+    assert_bit_equal(np.concatenate(parts), want, "row shards")
+
+
+def _load(backend, blob):
+    f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+    f.write(blob)
+    f.close()
+    try:
+        return backend.SparseOnnxModel(f.name)
+    finally:
+        os.unlink(f.name)
+
+
+def test_model_mlp_golden(backend, golden, cuda):
+    m = _load(backend, golden["mlp_onnx"].tobytes())
+    x_mem = golden["mlp_x_mem"]                              # [features][B] memory
+    B = x_mem.shape[1]
+    y = m.run(x_mem.reshape(B, -1))                          # labelled (B, N): only the bytes matter
+    assert list(y.shape) == golden["mlp_shape_ref"].tolist()
+    want = golden["mlp_y_mem_ref"]
+    # layers 1-2 are bit-exact; the final sigmoid/tanh differ from glibc by a few ulp
+    assert np.abs(y.ravel() - want).max() <= 1e-6
+    m2 = _load(backend, golden["mlp2_onnx"].tobytes())      # relu-only model: bit-exact end to end
+    x2 = golden["mlp2_x_mem"]
+    y2 = m2.run(x2.reshape(x2.shape[1], -1))
+    assert_bit_equal(y2.ravel(), golden["mlp2_y_mem_ref"], "relu MLP")
+
+
+def test_model_cnn_golden(backend, golden, cuda):
+    m = _load(backend, golden["cnn_onnx"].tobytes())
+    x_mem = golden["cnn_x_mem"]                              # [C,H,W,B]
+    B = x_mem.shape[3]
+    y = m.run(x_mem.reshape(B, *x_mem.shape[:3]))
+    assert list(y.shape) == golden["cnn_shape_ref"].tolist()
+    assert_bit_equal(y.ravel(), golden["cnn_y_mem_ref"], "conv-relu-conv-relu")
+
+
+def test_model_resize_and_device_run(backend, golden, orc, cuda):
+    m = _load(backend, golden["mlp2_onnx"].tobytes())
+    x_mem = golden["mlp2_x_mem"]
+    want = golden["mlp2_y_mem_ref"].reshape(-1, x_mem.shape[1])
+    m.resize_buffers(3)                                      # a different batch: first three columns
+    y3 = m.run(np.ascontiguousarray(x_mem[:, :3]).reshape(3, -1))
+    assert_bit_equal(y3.ravel().reshape(-1, 3), want[:, :3], "batch 3")
+    y5 = m.run(x_mem.reshape(5, -1))                         # back to 5: re-plans by itself
+    assert_bit_equal(y5.ravel().reshape(-1, 5), want, "batch 5")
+    dX = torch.from_numpy(x_mem).to(cuda)
+    dY = torch.empty(want.shape, device=cuda)
+    m.run_device(dX.data_ptr(), 5, dY.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), want, "device run")
+
+
+def test_model_scaled_config3_vs_oracle(backend, orc, cuda):
+    import onnx_wire
+    import workloads as wl
+    d = wl.cfg3(0.1)
+    m = _load(backend, onnx_wire.mlp_model(d["weights"], d["biases"], d["acts"], d["B"]))
+    x_mem = np.ascontiguousarray(d["x"].T)
+    y = m.run(x_mem.reshape(d["B"], -1)).ravel().reshape(-1, d["B"])
+    a = x_mem
+    for W, b, act in zip(d["weights"][:3], d["biases"][:3], (1, 1, 1)):
+        a = orc.spmm(orc.encode(W), a, b, act=act)
+    pre = orc.spmm(orc.encode(d["weights"][3]), a, d["biases"][3])
+    assert np.abs(y - orc.activation(pre, 2)).max() <= 1e-6
+    assert m.flops_per_run(d["B"]) == 2.0 * d["B"] * sum(int(np.count_nonzero(W)) for W in d["weights"])

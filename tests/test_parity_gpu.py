@@ -1,0 +1,316 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes) with device pointers, against
+the CPU oracle on the same seeded inputs and against the golden vectors of the reference binary.
+
+Bars: ELLPACK encodings, SpMM and conv outputs bit-exact (a thread owns whole output elements and
+runs the reference's FMA chain in storage order); SpMV within 1e-5 * (sum_j |w||x| + |bias|) per
+element (the summation order differs from the reference's 16 partial sums); sigmoid / tanh
+epilogues within 4 ulp-ish relative 1e-6 of the C library."""
+import numpy as np
+import pytest
+import torch
+
+import spx_ctypes as sx
+from conftest import assert_bit_equal
+
+pytestmark = pytest.mark.gpu
+
+SPMV_TOL = 1e-5   # times sum|w||x| + |bias|, stated by the acceptance contract
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def sparse(rng, m, n, p):
+    W = rng.standard_normal((m, n)).astype(np.float32)
+    W[rng.random((m, n)) >= p] = 0
+    return W
+
+
+def gpu_ell(lib, E):
+    return lib.ell_create(E.Wd, E.idx, E.nnz, E.n)
+
+
+def gpu_spmm(h, X, bias, act, cuda, ld_pad=0):
+    n, C = X.shape
+    ldx = C + ld_pad
+    Xp = np.zeros((n, ldx), np.float32)
+    Xp[:, :C] = X
+    dX = dev(Xp, cuda)
+    dB = None if bias is None else dev(bias, cuda)
+    dY = torch.full((h.m, ldx), float("nan"), device=cuda, dtype=torch.float32)
+    h.spmm(ptr(dX), C, ldx, ptr(dB), act, ptr(dY), ldx)
+    torch.cuda.synchronize()
+    return dY.cpu().numpy()[:, :C]
+
+
+def gpu_spmv(h, x, bias, cuda):
+    dx = dev(x, cuda)
+    dB = None if bias is None else dev(bias, cuda)
+    dy = torch.full((h.m,), float("nan"), device=cuda, dtype=torch.float32)
+    h.spmv(ptr(dx), ptr(dB), ptr(dy))
+    torch.cuda.synchronize()
+    return dy.cpu().numpy()
+
+
+# ---- golden vectors of the reference binary ---------------------------------------------------
+@pytest.mark.parametrize("name", ["mm_a", "mm_b", "mm_c", "mm_d"])
+def test_golden_spmm_spmv(lib, orc, golden, cuda, name):
+    E = orc.encode(golden[name + "_W"])
+    h = gpu_ell(lib, E)
+    Wd, idx, nnz = h.download()
+    assert_bit_equal(Wd, E.Wd, "Wd round trip")
+    assert np.array_equal(idx, E.idx) and np.array_equal(nnz, E.nnz)
+    X, b, x = golden[name + "_X"], golden[name + "_bias"], golden[name + "_x"]
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_NONE, cuda), golden[name + "_Y_ref"], "spmm")
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_RELU, cuda), golden[name + "_Yrelu_ref"], "spmm+relu")
+    assert_bit_equal(gpu_spmm(h, X, None, sx.ACT_NONE, cuda), golden[name + "_Ynobias_ref"], "spmm no bias")
+    bound = orc.absbound(E, x, b)
+    assert (np.abs(gpu_spmv(h, x, b, cuda) - golden[name + "_y_ref"]) <= SPMV_TOL * bound).all()
+    assert (np.abs(gpu_spmv(h, x, None, cuda) - golden[name + "_ynobias_ref"]) <= SPMV_TOL * orc.absbound(E, x, None)).all()
+
+
+@pytest.mark.parametrize("name", ["conv_a", "conv_b", "conv_c", "conv_d", "conv_e"])
+def test_golden_conv(lib, orc, golden, cuda, name):
+    B, Cin, Cout, H, W, k, pad, dil, relu = golden[name + "_geom"].tolist()
+    E = orc.encode(golden[name + "_weight"].reshape(Cout, -1))
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(Cin, Cout, k, k, H, W, pH=pad, pW=pad, dH=dil, dW=dil)
+    x = golden[name + "_x_nchw"]
+    dB = dev(golden[name + "_bias"], cuda)
+    for layout, src, want in ((sx.LAYOUT_PF, np.ascontiguousarray(x.transpose(1, 2, 3, 0)), golden[name + "_pf_ref"]),
+                              (sx.LAYOUT_NCHW, x, golden[name + "_nchw_ref"])):
+        dX = dev(src, cuda)
+        dY = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
+        h.conv2d(g, layout, ptr(dX), B, ptr(dB), sx.ACT_RELU if relu else sx.ACT_NONE, ptr(dY))
+        torch.cuda.synchronize()
+        assert_bit_equal(dY.cpu().numpy(), want, f"{name} layout {layout}")
+
+
+# ---- oracle parity on seeded inputs -----------------------------------------------------------
+SPMM_CASES = [
+    # (m, n, C, density)  -- the reference's tests/unit/test_matmul.py shapes and more
+    (16, 32, 1, 0.7), (16, 32, 10, 0.7), (16, 32, 100, 0.7), (64, 128, 10, 0.5), (128, 256, 20, 0.3),
+    (256, 512, 10, 0.1), (1, 1, 1, 1.0), (1, 1000, 1, 0.9), (1000, 1, 1, 0.9), (32, 32, 1, 0.0),
+    (10, 10, 1, 1.0), (10, 10, 10, 0.5), (10, 10, 10, 0.1), (20, 20, 10, 0.8), (100, 100, 10, 0.8),
+    (1000, 1000, 10, 0.9), (500, 500, 10, 0.95), (2000, 2000, 10, 0.7), (3000, 3000, 10, 0.6),
+    (300, 700, 256, 0.1), (257, 129, 260, 0.2), (64, 4096, 128, 0.1), (513, 300, 36, 0.15), (40, 50, 1024, 0.3),
+]
+
+
+@pytest.mark.parametrize("m,n,C,p", SPMM_CASES)
+def test_spmm_bit_exact_vs_oracle(lib, orc, cuda, m, n, C, p):
+    rng = np.random.default_rng([m, n, C])
+    W = sparse(rng, m, n, p)
+    X = rng.uniform(-1, 1, (n, C)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_NONE, cuda), orc.spmm(E, X, b), "spmm")
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_RELU, cuda, ld_pad=4), orc.spmm(E, X, b, act=1), "spmm relu, padded ld")
+    assert_bit_equal(gpu_spmm(h, X, None, sx.ACT_NONE, cuda, ld_pad=3), orc.spmm(E, X, None), "spmm odd ld")
+
+
+@pytest.mark.parametrize("act", [sx.ACT_SIGMOID, sx.ACT_TANH])
+def test_spmm_sigmoid_tanh_epilogue(lib, orc, cuda, act):
+    rng = np.random.default_rng(act)
+    W = sparse(rng, 200, 300, 0.1)
+    X = rng.uniform(-1, 1, (300, 64)).astype(np.float32)
+    b = rng.standard_normal(200).astype(np.float32)
+    E = orc.encode(W)
+    got = gpu_spmm(gpu_ell(lib, E), X, b, act, cuda)
+    want = orc.spmm(E, X, b, act=act)
+    # expf / tanhf of CUDA vs glibc differ by a few ulp; outputs are in (-1, 1)
+    assert np.abs(got - want).max() <= 4e-7
+
+
+SPMV_CASES = [(16, 32, 0.7), (64, 128, 0.5), (128, 256, 0.3), (256, 512, 0.1), (1, 1, 1.0), (1, 1000, 0.9),
+              (1000, 1, 0.9), (32, 32, 0.0), (10, 10, 1.0), (10, 10, 0.5), (20, 20, 0.8), (100, 100, 0.8),
+              (1000, 1000, 0.9), (500, 500, 0.95), (2000, 2000, 0.7), (3000, 3000, 0.6), (4096, 4096, 0.01),
+              (300, 20000, 0.05), (70, 70000, 0.02)]
+
+
+@pytest.mark.parametrize("m,n,p", SPMV_CASES)
+def test_spmv_within_tolerance(lib, orc, cuda, m, n, p):
+    rng = np.random.default_rng([m, n, 17])
+    W = sparse(rng, m, n, p)
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    for bias in (b, None):
+        got = gpu_spmv(h, x, bias, cuda)
+        want = orc.spmv(E, x, bias)
+        bound = orc.absbound(E, x, bias)
+        assert (np.abs(got - want) <= SPMV_TOL * bound + 0.0).all(), np.abs(got - want).max()
+    y64 = W.astype(np.float64) @ x.astype(np.float64) + b
+    assert (np.abs(gpu_spmv(h, x, b, cuda) - y64) <= SPMV_TOL * orc.absbound(E, x, b)).all()
+
+
+def test_padding_is_never_multiplied(lib, orc, cuda):
+    """Rows shorter than r: padding slots (Wd=0, idx=0) must not touch X[0], even if it is inf/NaN."""
+    rng = np.random.default_rng(5)
+    W = sparse(rng, 64, 96, 0.2)
+    W[:, 0] = 0.0                       # column 0 is referenced by padding only
+    W[3, :] = 1.0
+    W[3, 0] = 0.0
+    X = rng.uniform(-1, 1, (96, 8)).astype(np.float32)
+    X[0, :] = np.inf
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    got = gpu_spmm(h, X, None, sx.ACT_NONE, cuda)
+    assert np.isfinite(got).all()
+    assert_bit_equal(got, orc.spmm(E, X, None), "spmm with inf in an unreferenced row")
+    assert np.isfinite(gpu_spmv(h, X[:, 0].copy(), None, cuda)).all()
+
+
+def test_empty_and_degenerate_shapes(lib, orc, cuda):
+    z = lib.ell_create(np.zeros((0, 0), np.float32), np.zeros((0, 0), np.uint32), np.zeros(0, np.uint32), 0)
+    z.spmm(0, 0, 0, 0, sx.ACT_NONE, 0, 0)          # m = 0, C = 0: nothing to do, no error
+    z.spmv(0, 0, 0)
+    E = orc.encode(np.zeros((8, 5), np.float32))   # r = 0: output is the bias
+    h = gpu_ell(lib, E)
+    b = np.arange(8, dtype=np.float32)
+    X = np.ones((5, 3), np.float32)
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_NONE, cuda), np.repeat(b[:, None], 3, 1), "bias only")
+    assert_bit_equal(gpu_spmv(h, X[:, 0].copy(), b, cuda), b, "bias only spmv")
+    with pytest.raises(sx.SpxError):               # column id out of range is rejected at upload
+        lib.ell_create(np.ones((1, 1), np.float32), np.full((1, 1), 9, np.uint32), np.ones(1, np.uint32), 4)
+    with pytest.raises(sx.SpxError):
+        h.spmm(1, 3, 2, 0, sx.ACT_NONE, 1, 3)      # ldx < C
+
+
+def test_csr_and_device_encoder(lib, orc, cuda):
+    import workloads as wl
+    rng = np.random.default_rng(11)
+    W = sparse(rng, 300, 1000, 0.05)
+    W[7, :] = 0
+    W[9, 5] = -0.0
+    E = orc.encode(W)
+    rowptr, col, val = wl.csr_from_blocks([(0, W)], 300)
+    hc = lib.ell_create_csr(300, 1000, rowptr, col, val)
+    hd = lib.ell_encode_device(dev(W, cuda).data_ptr(), 300, 1000)
+    for h in (hc, hd):
+        Wd, idx, nnz = h.download()
+        assert h.r == E.r and h.nnz_total == int(E.nnz.sum())
+        assert_bit_equal(Wd, E.Wd, "Wd")
+        assert np.array_equal(idx, E.idx) and np.array_equal(nnz, E.nnz)
+    out = torch.empty((300, 1000), device=cuda, dtype=torch.float32)
+    lib.spx_ell_decode_device(hd.h, out.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert_bit_equal(out.cpu().numpy(), orc.decode(E), "device decode")
+
+
+CONV_CASES = [
+    # B, Cin, Cout, H, W, k, stride, pad, dil
+    (4, 8, 16, 12, 12, 3, 1, 1, 1), (32, 16, 24, 14, 14, 3, 1, 1, 1), (3, 5, 7, 9, 11, 3, 1, 0, 1),
+    (8, 16, 8, 10, 10, 1, 1, 0, 1), (2, 6, 6, 13, 9, 5, 1, 2, 1), (4, 8, 8, 12, 12, 3, 2, 1, 1),
+    (5, 4, 6, 11, 11, 3, 1, 2, 2), (16, 32, 32, 8, 8, 3, 1, 1, 1), (1, 3, 4, 6, 6, 3, 1, 1, 1),
+]
+
+
+@pytest.mark.parametrize("B,Cin,Cout,H,W,k,s,pad,dil", CONV_CASES)
+@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW])
+def test_conv_bit_exact_vs_oracle(lib, orc, cuda, layout, B, Cin, Cout, H, W, k, s, pad, dil):
+    rng = np.random.default_rng([B, Cin, Cout, H, k, s])
+    wt = sparse(rng, Cout, Cin * k * k, 0.25) * np.float32(0.3)
+    bias = rng.standard_normal(Cout).astype(np.float32)
+    x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
+    src = np.ascontiguousarray(x.transpose(1, 2, 3, 0)) if layout == sx.LAYOUT_PF else x
+    E = orc.encode(wt)
+    gd = dict(Cin=Cin, kH=k, kW=k, sH=s, sW=s, pH=pad, pW=pad, dH=dil, dW=dil, H=H, W=W)
+    want = orc.conv2d(E, gd, layout, src, B, bias, 1)
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(Cin, Cout, k, k, H, W, s, s, pad, pad, dil, dil)
+    dX, dB = dev(src, cuda), dev(bias, cuda)
+    dY = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
+    h.conv2d(g, layout, ptr(dX), B, ptr(dB), sx.ACT_RELU, ptr(dY))
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), want, "conv")
+    # and against a dense fp32 convolution (mathematical check, independent of the ELLPACK chain)
+    ref = torch.nn.functional.conv2d(torch.from_numpy(x), torch.from_numpy(wt.reshape(Cout, Cin, k, k)),
+                                     torch.from_numpy(bias), stride=s, padding=pad, dilation=dil).relu().numpy()
+    got = dY.cpu().numpy()
+    got_nchw = got.transpose(3, 0, 1, 2) if layout == sx.LAYOUT_PF else got
+    assert np.abs(got_nchw - ref).max() <= 1e-4
+
+
+def test_conv_rejects_bad_geometry(lib, orc, cuda):
+    E = orc.encode(np.ones((4, 18), np.float32))
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(2, 4, 3, 3, 8, 8, pH=1, pW=1)
+    g.Ho += 1
+    with pytest.raises(sx.SpxError):
+        h.conv2d(g, sx.LAYOUT_PF, 1, 1, 0, 0, 1)
+    g = sx.conv_geom(3, 4, 3, 3, 8, 8)            # Cin*9 != E.n
+    with pytest.raises(sx.SpxError):
+        h.conv2d(g, sx.LAYOUT_PF, 1, 1, 0, 0, 1)
+
+
+@pytest.mark.parametrize("op,fn", [(sx.OP_RELU, lambda a, b: np.maximum(a, 0)), (sx.OP_ADD, lambda a, b: a + b)])
+@pytest.mark.parametrize("count", [1, 7, 1024, 100003])
+def test_eltwise_exact(lib, cuda, op, fn, count):
+    rng = np.random.default_rng(count)
+    a = rng.standard_normal(count).astype(np.float32)
+    b = rng.standard_normal(count).astype(np.float32)
+    da, db = dev(a, cuda), dev(b, cuda)
+    out = torch.empty(count, device=cuda, dtype=torch.float32)
+    lib.spx_eltwise(op, da.data_ptr(), db.data_ptr(), out.data_ptr(), count, 0)
+    torch.cuda.synchronize()
+    assert_bit_equal(out.cpu().numpy(), fn(a, b).astype(np.float32), "eltwise")
+    lib.spx_eltwise(op, da.data_ptr(), db.data_ptr(), da.data_ptr(), count, 0)   # in place
+    torch.cuda.synchronize()
+    assert_bit_equal(da.cpu().numpy(), fn(a, b).astype(np.float32), "eltwise in place")
+
+
+def test_eltwise_sigmoid_tanh(lib, orc, cuda):
+    a = np.linspace(-12, 12, 5001).astype(np.float32)
+    for op, act in ((sx.OP_SIGMOID, 2), (sx.OP_TANH, 3)):
+        da = dev(a, cuda)
+        out = torch.empty_like(da)
+        lib.spx_eltwise(op, da.data_ptr(), 0, out.data_ptr(), a.size, 0)
+        torch.cuda.synchronize()
+        assert np.abs(out.cpu().numpy() - orc.activation(a, act)).max() <= 4e-7
+
+
+def test_host_buffer_entry_points(lib, orc, cuda):
+    rng = np.random.default_rng(23)
+    W = sparse(rng, 500, 400, 0.1)
+    X = rng.uniform(-1, 1, (400, 48)).astype(np.float32)
+    b = rng.standard_normal(500).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    assert_bit_equal(h.spmm_host(X, b), orc.spmm(E, X, b), "spmm_host")
+    assert_bit_equal(h.spmm_host(X, None, sx.ACT_RELU), orc.spmm(E, X, None, act=1), "spmm_host relu")
+    y = h.spmv_host(X[:, 0].copy(), b)
+    assert (np.abs(y - orc.spmv(E, X[:, 0].copy(), b)) <= SPMV_TOL * orc.absbound(E, X[:, 0].copy(), b)).all()
+    before = lib.spx_launch_count()
+    h.spmm_host(X, b)
+    assert lib.spx_launch_count() == before + 1
+
+
+def test_config1_scaled_and_linearity(lib, orc, cuda):
+    """Config 1 recipe at reduced size: oracle parity, plus linearity at the full size where the
+    oracle would take too long for a unit test: E(aX1 + X2) == a E X1 + E X2 within rounding."""
+    import workloads as wl
+    d = wl.cfg1(0.25)
+    E = orc.encode(d["W"])
+    h = gpu_ell(lib, E)
+    assert_bit_equal(gpu_spmm(h, d["X"], d["bias"], sx.ACT_NONE, cuda), orc.spmm(E, d["X"], d["bias"]), "cfg1/4")
+    full = wl.cfg1(1.0)
+    Ef = orc.encode(full["W"])
+    hf = gpu_ell(lib, Ef)
+    X1 = full["X"]
+    X2 = np.roll(X1, 1, axis=0)
+    lhs = gpu_spmm(hf, (2.0 * X1 + X2).astype(np.float32), None, sx.ACT_NONE, cuda)
+    rhs = 2.0 * gpu_spmm(hf, X1, None, sx.ACT_NONE, cuda) + gpu_spmm(hf, X2, None, sx.ACT_NONE, cuda)
+    scale = np.abs(full["W"]).sum(1, keepdims=True) * 3.0
+    assert (np.abs(lhs - rhs) <= 1e-5 * scale).all()
+    # row 0..63 of the full problem against the oracle (cheap slice of the same matrix)
+    sub = orc.encode(full["W"][:64])
+    assert_bit_equal(gpu_spmm(gpu_ell(lib, sub), X1, full["bias"][:64], sx.ACT_NONE, cuda),
+                     orc.spmm(sub, X1, full["bias"][:64]), "cfg1 rows 0..63")
