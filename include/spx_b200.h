@@ -135,6 +135,19 @@ int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void
  * conv2d_tiled_im2col_fmajor / conv2d_rbm_fmajor_implicit (src/layers/conv_kernels.cpp:66-470). */
 int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                const float* bias, int act, float* out, void* stream);
+/* spx_conv2d for callers that must not allocate device memory (no counterpart in the
+ * reference, which runs on the CPU).  Some hosts hand all device memory to their own pool at
+ * start-up, so a later cudaMalloc has nothing to take, and a latency-bound serving loop cannot
+ * accept the device-wide synchronisation an allocation may imply.  spx_conv2d allocates a tap
+ * table per handle on first use; this variant keeps that table in a fixed 4 MiB array inside the
+ * library image instead (held by every GPU that loads the library until the process exits) and
+ * calls no cudaMalloc / cudaFree or allocating routine.  Limits and rules: Cout * (r rounded up
+ * to 32) must not exceed 1 048 576 slots, else SPX_ERR_LIMIT; the handle's device must be
+ * current; all calls share the one array, so calls that overlap on the GPU race -- serialise
+ * them; the first call on a device looks up the array's address and should come before any
+ * stream capture.  Same arguments and results as spx_conv2d. */
+int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
+                      const float* bias, int act, float* out, void* stream);
 /* out = op(a[, b]) elementwise; replaces applyRelu/Sigmoid/Tanh (src/layers/activation.cpp:3-62),
  * relu/sigmoid/tanh_inplace (src/activations.cpp:20-68) and applyAdd (src/layers/add.cpp:9-76).
  * out may alias a. */

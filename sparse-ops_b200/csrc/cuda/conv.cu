@@ -130,3 +130,95 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
 }
 
 }  // namespace spx
+
+// ---------------------------------------------------------------------------------------------
+// spx_conv2d_static: the same convolution for callers that must not allocate device memory.
+//
+// Who cannot allocate: a host program that gives the whole device memory to its own pool at
+// start-up (typical for inference servers) has nothing left for a later cudaMalloc, and a
+// latency-bound serving loop cannot afford the device-wide synchronisation an allocation or a
+// free may imply.  spx_conv2d allocates once per handle (its tap table).  This variant keeps
+// the tap table in a fixed array that is part of the library image instead, so the call
+// itself never allocates or frees anything: no cudaMalloc / cudaFree, no allocating library
+// routine.  The price: every GPU that loads the library holds the array (4 MiB) until the
+// process exits, and a weight matrix whose padded slab (Cout * pitch) has more slots than the
+// array is rejected with SPX_ERR_LIMIT.
+//
+// The array is shared by all calls and keeps the previous call's contents.  Each call first
+// rewrites the slots its own convolution reads (nothing has to start at zero), but two calls
+// that overlap on the GPU (different streams or threads) would overwrite each other's table:
+// serialise them.  The first call on a device looks the array's device address up
+// (cudaGetSymbolAddress); make that first call before any stream capture begins.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+constexpr uint32_t kStaticTapSlots = 1u << 20;          // 4 MiB of uint32 slots
+static __device__ __align__(256) uint32_t spx_static_taps[kStaticTapSlots];
+
+// In host code `spx_static_taps` is only a handle for the runtime, not a device address.  The
+// address is fetched once per device, with that device current, and cached.
+static int static_taps_address(int device, uint32_t** out)
+{
+    static std::mutex mu;
+    static uint32_t* cached[64] = {};
+    if (device < 0 || device >= 64) return spx::fail(SPX_ERR_LIMIT, "conv2d_static: device ordinal %d not supported", device);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cached[device]) {
+        void* p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, spx_static_taps);
+        if (err != cudaSuccess || !p)
+            return spx::fail(SPX_ERR_CUDA, "conv2d_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+        cached[device] = static_cast<uint32_t*>(p);
+    }
+    *out = cached[device];
+    return SPX_OK;
+}
+
+extern "C" int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
+                                 const float* bias, int act, float* out, void* stream)
+{
+    using spx::fail;
+    if (!e || !g) return fail(SPX_ERR_ARG, "handle / geometry is null");
+    if (layout != SPX_LAYOUT_PF && layout != SPX_LAYOUT_NCHW) return fail(SPX_ERR_ARG, "unknown layout %d", layout);
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (g->sH == 0 || g->sW == 0 || g->dH == 0 || g->dW == 0 || g->kH == 0 || g->kW == 0)
+        return fail(SPX_ERR_ARG, "stride, dilation and kernel extent must be positive");
+    if (e->m != g->Cout) return fail(SPX_ERR_ARG, "ELLPACK rows (%u) != Cout (%u)", e->m, g->Cout);
+    if ((uint64_t)g->Cin * g->kH * g->kW != e->n) return fail(SPX_ERR_ARG, "ELLPACK columns (%u) != Cin*kH*kW", e->n);
+    const uint32_t eh = g->dH * (g->kH - 1) + 1, ew = g->dW * (g->kW - 1) + 1;
+    if (g->H + 2 * g->pH < eh || g->W + 2 * g->pW < ew) return fail(SPX_ERR_ARG, "kernel larger than padded input");
+    if (g->Ho != (g->H + 2 * g->pH - eh) / g->sH + 1 || g->Wo != (g->W + 2 * g->pW - ew) / g->sW + 1)
+        return fail(SPX_ERR_ARG, "Ho / Wo inconsistent with the geometry");
+    if (g->kH > 255 || g->kW > 255 || g->Cin > 65535)
+        return fail(SPX_ERR_LIMIT, "conv2d_static: kernel extent > 255 or Cin > 65535 not supported");
+    if (B == 0 || e->m == 0 || g->Ho == 0 || g->Wo == 0) return SPX_OK;
+    if (!in || !out) return fail(SPX_ERR_ARG, "in / out is null");
+    const uint64_t slots = (uint64_t)e->m * e->pitch;
+    if (slots > kStaticTapSlots)
+        return fail(SPX_ERR_LIMIT, "conv2d_static: weight slab has %llu slots (Cout * padded row length), the fixed "
+                    "tap table holds %u; use spx_conv2d", (unsigned long long)slots, kStaticTapSlots);
+    int cur = -1;
+    SPX_CUDA(cudaGetDevice(&cur));
+    if (cur != e->device)
+        return fail(SPX_ERR_ARG, "conv2d_static: the handle's device (%d) must be current (current: %d)", e->device, cur);
+    uint32_t* taps = nullptr;
+    int rc = static_taps_address(cur, &taps);
+    if (rc != SPX_OK) return rc;
+
+    cudaStream_t s = (cudaStream_t)stream;
+    if (e->r) {
+        build_taps_kernel<<<e->m, 128, 0, s>>>(e->idx, e->nnz, e->m, e->pitch, g->kH, g->kW, taps);
+        SPX_LAUNCH_CHECK("build_taps_kernel");
+    }
+    ConvParams p{g->Cin, g->Cout, g->kH, g->kW, g->sH, g->sW, g->pH, g->pW, g->dH, g->dW, g->H, g->W, g->Ho, g->Wo, B};
+    const uint64_t per_m = (uint64_t)g->Ho * g->Wo * B;
+    const uint64_t gx = (per_m + 255) / 256;
+    if (gx > 0x7fffffffull || e->m > 65535) return fail(SPX_ERR_LIMIT, "conv2d_static: output too large for one launch");
+    dim3 grid((unsigned)gx, e->m);
+    if (layout == SPX_LAYOUT_PF)
+        conv_direct_kernel<SPX_LAYOUT_PF><<<grid, 256, 0, s>>>(e->Wd, taps, e->nnz, e->pitch, p, in, bias, act, out);
+    else
+        conv_direct_kernel<SPX_LAYOUT_NCHW><<<grid, 256, 0, s>>>(e->Wd, taps, e->nnz, e->pitch, p, in, bias, act, out);
+    SPX_LAUNCH_CHECK("conv_direct_kernel");
+    return SPX_OK;
+}
