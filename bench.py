@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
     ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
+    ap.add_argument("--rows", type=int, default=0, help="cfg5_spmm: override the row count (profiling on a smaller case)")
+    ap.add_argument("--cols", type=int, default=0, help="cfg5_spmm: override C, the dense column count")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     return ap.parse_args()
@@ -159,6 +161,10 @@ def build_workload(args, rank: int, world: int):
         m = max(4096 * world, int(262144 * s) // (4096 * world) * 4096 * world)
         n = max(1024, int(65536 * s))
         C = max(16, int(1024 * s) // 4 * 4)
+        if args.rows:
+            m = max(4096 * world, args.rows // (4096 * world) * 4096 * world)
+        if args.cols:
+            C = args.cols
         kmax = min(2048, n // 2)
         per = m // world
         rowptr, col, val = wl.cfg5_rows(rank * per, per, n=n, kmax=kmax, mean=64.0 if kmax >= 512 else kmax / 8)
