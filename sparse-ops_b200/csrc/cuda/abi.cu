@@ -75,6 +75,20 @@ int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out)
     return SPX_OK;
 }
 
+int set_row_order(spx_ell* e, const uint32_t* host_nnz)
+{
+    if (e->m == 0) return SPX_OK;
+    // counting sort by row length, longest first; stable, so ties keep ascending row id
+    std::vector<uint64_t> start((size_t)e->r + 2, 0);
+    for (uint32_t i = 0; i < e->m; ++i) start[e->r - host_nnz[i] + 1]++;
+    for (size_t k = 1; k < start.size(); ++k) start[k] += start[k - 1];
+    std::vector<uint32_t> order(e->m);
+    for (uint32_t i = 0; i < e->m; ++i) order[start[e->r - host_nnz[i]]++] = i;
+    if (!e->row_order) SPX_CUDA(cudaMalloc(&e->row_order, (size_t)e->m * sizeof(uint32_t)));
+    SPX_CUDA(cudaMemcpy(e->row_order, order.data(), (size_t)e->m * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    return SPX_OK;
+}
+
 // Device scratch owned by a handle for the host-buffer entry points.
 static int ensure_stage(spx_ell* e, size_t bytes)
 {
@@ -259,6 +273,8 @@ int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const ui
         spx_ell_destroy(e);
         return fail(SPX_ERR_CUDA, "ELLPACK upload failed: %s", cudaGetErrorString(err));
     }
+    rc = set_row_order(e, nnz);
+    if (rc != SPX_OK) { spx_ell_destroy(e); return rc; }
     *out = e;
     return SPX_OK;
 }
@@ -308,6 +324,10 @@ int spx_ell_create_csr(uint32_t m, uint32_t n, const uint64_t* rowptr, const uin
             return rc != SPX_OK ? rc : fail(err == cudaErrorMemoryAllocation ? SPX_ERR_OOM : SPX_ERR_CUDA,
                                             "CSR upload failed: %s", cudaGetErrorString(err));
         }
+        std::vector<uint32_t> counts(m);
+        for (uint32_t i = 0; i < m; ++i) counts[i] = (uint32_t)(rowptr[i + 1] - rowptr[i]);
+        rc = set_row_order(e, counts.data());
+        if (rc != SPX_OK) { spx_ell_destroy(e); return rc; }
     }
     *out = e;
     return SPX_OK;
@@ -325,7 +345,7 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
-    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->taps); cudaFree(e->stage_dev);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->stage_dev);
     delete e;
     return SPX_OK;
 }

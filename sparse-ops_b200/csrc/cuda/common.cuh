@@ -22,6 +22,10 @@ struct spx_ell {
     float* Wd = nullptr;         // m * pitch floats
     uint32_t* idx = nullptr;     // m * pitch column ids
     uint32_t* nnz = nullptr;     // m counts
+    // Row schedule: row ids sorted by descending nnz (ties by ascending id).  Kernels that give a
+    // warp one row take rows in this order, so the warps of a CTA get rows of equal length
+    // (no warp idles behind a long row) and the longest rows start first.
+    uint32_t* row_order = nullptr;   // m row ids
     // Lazily built, cached conv tap table: idx decoded to packed (cin, kh, kw) for one
     // kernel shape (conv.cu); keyed by (kH, kW).
     uint32_t* taps = nullptr;
@@ -85,4 +89,6 @@ int decode_device(const spx_ell* e, float* dW, cudaStream_t s);
 int csr_to_ell_device(spx_ell* e, const uint64_t* d_rowptr, const uint32_t* d_col, const float* d_val,
                       cudaStream_t s);
 int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out);
+// Builds e->row_order from host row counts (counting sort by length) and uploads it.
+int set_row_order(spx_ell* e, const uint32_t* host_nnz);
 }  // namespace spx

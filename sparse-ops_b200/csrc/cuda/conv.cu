@@ -14,6 +14,9 @@
 // kernel implements the mathematically correct stride).
 #include "common.cuh"
 
+#include <algorithm>
+#include <cstdlib>
+
 namespace {
 
 // Per-nonzero tap table: idx k decoded once per kernel shape to cin<<16 | kh<<8 | kw.
@@ -90,6 +93,146 @@ conv_direct_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ ta
     out[o] = acc;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// conv_pf_tile_kernel: the fast path for the [C,H,W,B] layout with B % 4 == 0.
+//
+// A CTA owns a tile of 4 x 8 output positions x BT batch entries x 16 output channels (one warp
+// per output channel, accumulators in registers for the whole kernel).  It walks the input
+// channels in chunks: the chunk's input patch (CC channels x the tile's receptive field x BT) is
+// staged in shared memory with 16-byte cp.async copies, positions outside the image are stored as
+// zeros (so a tap there contributes the operand 0.0f exactly like the reference's zero-filled
+// im2col tile), and every warp then consumes the nonzeros of its weight row whose input channel
+// lies in the chunk -- they are contiguous because rows are sorted by k = (cin, kh, kw).
+// Per nonzero: (w, tap offset) are read coalesced 32 at a time and broadcast with two shuffles,
+// then QB float4 shared-memory loads feed 4*QB FMAs per lane.  A quarter-warp always reads 128
+// contiguous bytes, so the loads are bank-conflict free for stride 1.
+//
+// Bound: one 4-byte operand per FMA from shared memory = 128 B/clk/SM = 32 FMA/clk/SM, a quarter
+// of the FP32 peak; HBM traffic is the input once per 16 output channels plus the output once.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTileH = 4, kTileW = 8, kTileWarps = 16;
+
+struct TileParams {
+    ConvParams c;
+    uint32_t BT;        // batch entries per CTA (multiple of 4, <= 32)
+    uint32_t CC;        // input channels per staged chunk
+    uint32_t THin, TWin;
+    uint32_t tilesX;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+template <int QB, int MINB>   // QB: float4 groups per lane = BT / 4; MINB: CTAs per SM aimed for
+__global__ void __launch_bounds__(kTileWarps * 32, MINB)
+conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ taps,
+                    const uint32_t* __restrict__ nnz, uint32_t pitch, TileParams tp,
+                    const float* __restrict__ in, const float* __restrict__ bias, int act,
+                    float* __restrict__ out)
+{
+    extern __shared__ __align__(16) float tile[];
+    const ConvParams& p = tp.c;
+    const uint32_t BT = QB * 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t ty = blockIdx.x / tp.tilesX, tx = blockIdx.x % tp.tilesX;
+    const uint32_t oh0 = ty * kTileH, ow0 = tx * kTileW;
+    const uint32_t b0 = blockIdx.z * BT;
+    const uint32_t mo = blockIdx.y * kTileWarps + warp;
+    const bool active = mo < p.Cout;
+    const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;      // image row of staged row 0
+    const int iw0 = (int)(ow0 * p.sW) - (int)p.pW;
+    const uint32_t rowUnits = tp.TWin * QB;             // float4 units per staged row
+    const uint32_t chanFloats = tp.THin * tp.TWin * BT;
+
+    // this lane's QB output positions: unit q = lane + 32 g -> (pixel, batch quad)
+    uint32_t off[QB];
+#pragma unroll
+    for (int g = 0; g < QB; ++g) {
+        const uint32_t q = lane + 32u * g;
+        const uint32_t pix = q / QB, quad = q % QB;
+        const uint32_t py = pix / kTileW, px = pix % kTileW;
+        off[g] = ((py * p.sH) * tp.TWin + px * p.sW) * BT + quad * 4;
+    }
+    const float bv = (active && bias) ? __ldg(bias + mo) : 0.0f;
+    float4 acc[QB];
+#pragma unroll
+    for (int g = 0; g < QB; ++g) acc[g] = make_float4(bv, bv, bv, bv);
+
+    const uint32_t nn = active ? __ldg(nnz + mo) : 0u;
+    const float* __restrict__ wrow = Wd + (size_t)(active ? mo : 0) * pitch;
+    const uint32_t* __restrict__ trow = taps + (size_t)(active ? mo : 0) * pitch;
+    uint32_t pos = 0;
+
+    for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC) {
+        const uint32_t c1 = min(p.Cin, c0 + tp.CC);
+        // ---- stage the chunk: one warp per (channel, row) of the patch ----
+        const uint32_t rows = (c1 - c0) * tp.THin;
+        for (uint32_t r = warp; r < rows; r += kTileWarps) {
+            const uint32_t c = r / tp.THin, y = r % tp.THin;
+            const int ih = ih0 + (int)y;
+            const bool rowok = (unsigned)ih < p.H;
+            float* srow = tile + (size_t)r * rowUnits * 4;
+            const float* grow = in + (((size_t)(c0 + c) * p.H + (rowok ? ih : 0)) * p.W) * p.B + b0;
+            for (uint32_t u = lane; u < rowUnits; u += 32) {
+                const uint32_t x = u / QB, q = u % QB;
+                const int iw = iw0 + (int)x;
+                if (rowok && (unsigned)iw < p.W) cp_async16(srow + u * 4, grow + (size_t)iw * p.B + q * 4);
+                else *reinterpret_cast<float4*>(srow + u * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        // ---- consume this row's nonzeros whose input channel is in [c0, c1) ----
+        if (active) {
+            for (;;) {
+                float wl = 0.0f;
+                uint32_t tl = 0, cin = 0xffffffffu;
+                if (pos + lane < nn) {
+                    wl = __ldg(wrow + pos + lane);
+                    const uint32_t t = __ldg(trow + pos + lane);
+                    cin = t >> 16;
+                    tl = (((cin - c0) * tp.THin + ((t >> 8) & 0xffu) * p.dH) * tp.TWin + (t & 0xffu) * p.dW) * BT;
+                }
+                const uint32_t cnt = __popc(__ballot_sync(0xffffffffu, cin < c1));   // a prefix: rows are sorted by k
+                for (uint32_t t = 0; t < cnt; ++t) {
+                    const float wt = __shfl_sync(0xffffffffu, wl, t);
+                    const float* xs = tile + __shfl_sync(0xffffffffu, tl, t);
+#pragma unroll
+                    for (int g = 0; g < QB; ++g) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xs + off[g]);
+                        acc[g].x = fmaf(wt, xv.x, acc[g].x);
+                        acc[g].y = fmaf(wt, xv.y, acc[g].y);
+                        acc[g].z = fmaf(wt, xv.z, acc[g].z);
+                        acc[g].w = fmaf(wt, xv.w, acc[g].w);
+                    }
+                }
+                pos += cnt;
+                if (cnt < 32) break;
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+#pragma unroll
+    for (int g = 0; g < QB; ++g) {
+        const uint32_t q = lane + 32u * g;
+        const uint32_t pix = q / QB, quad = q % QB;
+        const uint32_t oh = oh0 + pix / kTileW, ow = ow0 + pix % kTileW;
+        if (oh < p.Ho && ow < p.Wo) {
+            float4 o = acc[g];
+            if (act != SPX_ACT_NONE) {
+                o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
+                o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
+            }
+            *reinterpret_cast<float4*>(out + (((size_t)mo * p.Ho + oh) * p.Wo + ow) * p.B + b0 + quad * 4) = o;
+        }
+    }
+}
+
 }  // namespace
 
 namespace spx {
@@ -106,6 +249,72 @@ static int ensure_taps(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
     return SPX_OK;
 }
 
+template <int QB, int MINB>
+static int launch_tile_qb(const spx_ell* e, const TileParams& tp, dim3 grid, size_t smem, const float* in,
+                          const float* bias, int act, float* out, cudaStream_t s)
+{
+    auto kfn = conv_pf_tile_kernel<QB, MINB>;
+    cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    kfn<<<grid, kTileWarps * 32, smem, s>>>(e->Wd, e->taps, e->nnz, e->pitch, tp, in, bias, act, out);
+    SPX_LAUNCH_CHECK("conv_pf_tile_kernel");
+    return SPX_OK;
+}
+
+// Returns -1 when the shape is not covered (caller falls back to the direct kernel).
+static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const float* in, const float* bias, int act,
+                               float* out, cudaStream_t s)
+{
+    static const bool disabled = [] { const char* v = getenv("SPX_CONV_DIRECT"); return v && v[0] == '1'; }();
+    if (disabled) return -1;
+    if (p.B % 4 != 0) return -1;
+    if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+    // batch entries per CTA: the largest multiple of 4 that divides B and is <= 32
+    uint32_t BT = 0;
+    for (uint32_t c = 32; c >= 4; c -= 4) if (p.B % c == 0) { BT = c; break; }
+    if (!BT) return -1;
+    TileParams tp{};
+    tp.c = p;
+    tp.BT = BT;
+    tp.THin = (kTileH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
+    tp.TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
+    const size_t chanBytes = (size_t)tp.THin * tp.TWin * BT * sizeof(float);
+    static const int ctas = [] { const char* v = getenv("SPX_CONV_CTAS"); return v ? atoi(v) : 0; }();
+    // Two CTAs per SM overlap one CTA's staging with the other's FMAs; with 8 float4 groups per
+    // lane (batch 32) the accumulators need more than the 64 registers that allows.
+    const int per_sm = ctas == 1 || ctas == 2 ? ctas : (BT / 4 > 4 ? 1 : 2);
+    const size_t budget = per_sm == 2 ? 100 * 1024 : 200 * 1024;
+    if (chanBytes > budget) return -1;
+    tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
+    // the per-nonzero shared-memory offset must fit 32 bits (it does: <= budget / 4)
+    tp.tilesX = (p.Wo + kTileW - 1) / kTileW;
+    const uint32_t tilesY = (p.Ho + kTileH - 1) / kTileH;
+    const uint64_t tiles = (uint64_t)tp.tilesX * tilesY;
+    const uint32_t gy = (p.Cout + kTileWarps - 1) / kTileWarps, gz = p.B / BT;
+    if (tiles > 0x7fffffffull || gy > 65535 || gz > 65535) return -1;
+    dim3 grid((unsigned)tiles, gy, gz);
+    const size_t smem = chanBytes * tp.CC;
+    switch (BT / 4) {
+    case 1: return per_sm == 2 ? launch_tile_qb<1, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<1, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 2: return per_sm == 2 ? launch_tile_qb<2, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<2, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 3: return per_sm == 2 ? launch_tile_qb<3, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<3, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 4: return per_sm == 2 ? launch_tile_qb<4, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<4, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 5: return per_sm == 2 ? launch_tile_qb<5, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<5, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 6: return per_sm == 2 ? launch_tile_qb<6, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<6, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 7: return per_sm == 2 ? launch_tile_qb<7, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<7, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    case 8: return per_sm == 2 ? launch_tile_qb<8, 2>(e, tp, grid, smem, in, bias, act, out, s)
+                           : launch_tile_qb<8, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    }
+    return -1;
+}
+
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                   const float* bias, int act, float* out, cudaStream_t s)
 {
@@ -116,6 +325,10 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     if (rc != SPX_OK) return rc;
     ConvParams p{g->Cin, g->Cout, g->kH, g->kW, g->sH, g->sW, g->pH, g->pW, g->dH, g->dW,
                  g->H, g->W, g->Ho, g->Wo, B};
+    if (layout == SPX_LAYOUT_PF && e->r) {
+        int rc2 = launch_conv_pf_tile(e, p, in, bias, act, out, s);
+        if (rc2 != -1) return rc2;           // -1: shape not covered by the tiled kernel
+    }
     const uint64_t per_m = (uint64_t)g->Ho * g->Wo * B;
     const uint64_t gx = (per_m + 255) / 256;
     if (gx > 0x7fffffffull || e->m > 65535)

@@ -128,6 +128,8 @@ int encode_device(const float* dW, uint32_t m, uint32_t n, cudaStream_t s, spx_e
         for (uint32_t v : h) tot += v;
         e->nnz_total = tot;
         e->max_nnz = r;
+        rc = set_row_order(e, h.data());
+        if (rc != SPX_OK) { spx_ell_destroy(e); return rc; }
     }
     *out = e;
     return SPX_OK;

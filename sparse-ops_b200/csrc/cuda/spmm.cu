@@ -17,6 +17,8 @@
 //                  that fall in the staged block.  Removes the L2 gather traffic.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int kGatherWarps = 8;
@@ -33,16 +35,18 @@ __device__ __forceinline__ void fma4(float4& a, float w, const float4& x) {
 // ---------------------------------------------------------------------------------------
 // spmm_gather<NV>: lane owns NV float4 groups: columns c0 + v*128 + 4*lane .. +3.
 // ---------------------------------------------------------------------------------------
-template <int NV>
+template <int NV, int G>
 __global__ void __launch_bounds__(kGatherWarps * 32)
 spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
-                const uint32_t* __restrict__ nnz, uint32_t m, uint32_t pitch,
+                const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                uint32_t m, uint32_t pitch,
                 const float* __restrict__ X, uint32_t C, uint64_t ldx,
                 const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
-    if (row >= m) return;                       // whole warp leaves together
+    const uint32_t slot = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
+    if (slot >= m) return;                      // whole warp leaves together
+    const uint32_t row = __ldg(row_order + slot);   // rows by descending length: equal work per CTA
     const uint32_t c0 = blockIdx.y * (128u * NV) + 4u * lane;
     bool on[NV];
 #pragma unroll
@@ -65,11 +69,11 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
             kl = __ldg(k + j0 + lane);
         }
         const uint32_t cnt = min(32u, nn - j0);
-        for (uint32_t t0 = 0; t0 < cnt; t0 += 8) {
-            float wt[8];
-            float4 xv[8][NV];
+        for (uint32_t t0 = 0; t0 < cnt; t0 += G) {
+            float wt[G];
+            float4 xv[G][NV];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {       // issue all gathers of the group first
+            for (int u = 0; u < G; ++u) {       // issue all gathers of the group first
                 wt[u] = __shfl_sync(0xffffffffu, wl, (t0 + u) & 31);
                 const uint32_t kt = __shfl_sync(0xffffffffu, kl, (t0 + u) & 31);
                 const float* xr = X + (size_t)kt * ldx + c0;
@@ -79,7 +83,7 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                     xv[u][v] = (live && on[v]) ? ldg4(xr + 128 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {       // then the FMA chain, strictly in storage order
+            for (int u = 0; u < G; ++u) {       // then the FMA chain, strictly in storage order
                 if ((t0 + u) < cnt) {
 #pragma unroll
                     for (int v = 0; v < NV; ++v) fma4(acc[v], wt[u], xv[u][v]);
@@ -104,13 +108,15 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
 template <int NV>
 __global__ void __launch_bounds__(kGatherWarps * 32)
 spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
-                   const uint32_t* __restrict__ nnz, uint32_t m, uint32_t pitch,
+                   const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                   uint32_t m, uint32_t pitch,
                    const float* __restrict__ X, uint32_t C, uint64_t ldx,
                    const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
-    if (row >= m) return;
+    const uint32_t slot = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
+    if (slot >= m) return;
+    const uint32_t row = __ldg(row_order + slot);
     const uint32_t c0 = blockIdx.y * (32u * NV) + lane;
     bool on[NV];
 #pragma unroll
@@ -163,6 +169,20 @@ spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ id
 
 namespace spx {
 
+// Column-panel width of the gather kernel.  All CTAs in flight work on one panel of X
+// (n rows x 128*NV columns); it must stay L2-resident while every row of E gathers from it.
+// SPX_SPMM_NV=1|2 overrides the choice (tuning knob).
+static int gather_nv(uint32_t n, uint32_t C)
+{
+    static const int forced = [] { const char* v = getenv("SPX_SPMM_NV"); return v ? atoi(v) : 0; }();
+    if (forced == 1 || forced == 2) return C > 128 ? forced : 1;
+    (void)n;
+    // Measured on B200 (262144 x 65536, C = 1024): 256-column panels beat 128-column ones
+    // (4.5 ms against 5.4 ms) even though the 67 MB panel no longer fits the near L2 partition:
+    // the (w, idx) broadcast is amortised over twice the columns.
+    return C > 128 ? 2 : 1;
+}
+
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s)
 {
@@ -172,25 +192,24 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     const uint32_t gx = (e->m + kGatherWarps - 1) / kGatherWarps;
     if (vec_ok) {
-        // Two float4 per lane (256-column panels) once C is wide enough to fill them.
-        if (C > 128) {
+        if (gather_nv(e->n, C) == 2) {
             dim3 grid(gx, (C + 255) / 256);
-            spmm_gather_vec<2><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->m, e->pitch,
-                                                                 X, C, ldx, bias, act, Y, ldy);
+            spmm_gather_vec<2, 4><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                                    X, C, ldx, bias, act, Y, ldy);
         } else {
             dim3 grid(gx, (C + 127) / 128);
-            spmm_gather_vec<1><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->m, e->pitch,
-                                                                 X, C, ldx, bias, act, Y, ldy);
+            spmm_gather_vec<1, 8><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                                    X, C, ldx, bias, act, Y, ldy);
         }
         SPX_LAUNCH_CHECK("spmm_gather_vec");
     } else {
         if (C > 32) {
             dim3 grid(gx, (C + 63) / 64);
-            spmm_gather_scalar<2><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->m, e->pitch,
+            spmm_gather_scalar<2><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
                                                                     X, C, ldx, bias, act, Y, ldy);
         } else {
             dim3 grid(gx, 1);
-            spmm_gather_scalar<1><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->m, e->pitch,
+            spmm_gather_scalar<1><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
                                                                     X, C, ldx, bias, act, Y, ldy);
         }
         SPX_LAUNCH_CHECK("spmm_gather_scalar");
