@@ -146,7 +146,6 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
     const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;      // image row of staged row 0
     const int iw0 = (int)(ow0 * p.sW) - (int)p.pW;
     const uint32_t rowUnits = tp.TWin * QB;             // float4 units per staged row
-    const uint32_t chanFloats = tp.THin * tp.TWin * BT;
 
     // this lane's QB output positions: unit q = lane + 32 g -> (pixel, batch quad)
     uint32_t off[QB];

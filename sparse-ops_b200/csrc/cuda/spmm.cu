@@ -7,16 +7,17 @@
 // output elements, so the result is bit-identical to the reference for every C, and no
 // padding slot is ever multiplied.
 //
-// Two kernels:
-//   spmm_gather  : warp per row, lanes across dense columns, X rows gathered through L1/L2.
-//                  Any shape.  Column panels are the slow grid dimension so that all CTAs in
-//                  flight work on the same X panel (which then stays in L2).
-//   spmm_kblock  : for X panels that fit shared memory block by block: a CTA owns a tile of
-//                  rows x 64 columns, walks the column-index range in blocks of KB rows of X
-//                  staged in shared memory, and every row consumes its (ascending) nonzeros
-//                  that fall in the staged block.  Removes the L2 gather traffic.
+// Kernel: spmm_gather -- warp per row, lanes across dense columns, X rows gathered through L1/L2.
+// Column panels are the slow grid dimension so that all CTAs in flight work on the same X panel.
+// Rows are taken from the handle's sorted row schedule (longest first), so the warps of a CTA
+// and the CTAs of a wave carry equal work.  Because every row walks its column ids in ascending
+// order, the warps resident on an SM sweep X roughly in step and share its rows through L1
+// (56 % L1 hit rate measured on a 4096 x 4096, 10 % dense matrix) -- staging X in shared memory
+// block by block was tried and was slower (staging, barriers and predicated tails cost more than
+// the L1 misses they removed).
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 
 namespace {
@@ -44,7 +45,7 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
-    const uint32_t slot = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
+    const uint32_t slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (slot >= m) return;                      // whole warp leaves together
     const uint32_t row = __ldg(row_order + slot);   // rows by descending length: equal work per CTA
     const uint32_t c0 = blockIdx.y * (128u * NV) + 4u * lane;
@@ -114,7 +115,7 @@ spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ id
                    const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
-    const uint32_t slot = blockIdx.x * kGatherWarps + (threadIdx.x >> 5);
+    const uint32_t slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (slot >= m) return;
     const uint32_t row = __ldg(row_order + slot);
     const uint32_t c0 = blockIdx.y * (32u * NV) + lane;
@@ -183,6 +184,19 @@ static int gather_nv(uint32_t n, uint32_t C)
     return C > 128 ? 2 : 1;
 }
 
+// Warps (= rows) per CTA.  Large problems use 8; small ones use fewer so that the grid still has
+// several CTAs per SM and the last wave is not mostly empty (a 4096-row matrix with 8 rows per CTA
+// left the SMs idle 40 % of the kernel's duration).
+static uint32_t gather_wpb(const spx_ell* e, uint32_t panels)
+{
+    static const int forced = [] { const char* v = getenv("SPX_SPMM_WPB"); return v ? atoi(v) : 0; }();
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return (uint32_t)forced;
+    const uint64_t want = (uint64_t)sm_count(e->device) * 8;
+    for (uint32_t wpb : {8u, 4u, 2u})
+        if ((uint64_t)((e->m + wpb - 1) / wpb) * panels >= want) return wpb;
+    return 2;
+}
+
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s)
 {
@@ -190,28 +204,29 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
     const bool vec_ok = (C % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
                         ((reinterpret_cast<uintptr_t>(X) & 15) == 0) &&
                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
-    const uint32_t gx = (e->m + kGatherWarps - 1) / kGatherWarps;
     if (vec_ok) {
-        if (gather_nv(e->n, C) == 2) {
-            dim3 grid(gx, (C + 255) / 256);
-            spmm_gather_vec<2, 4><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                    X, C, ldx, bias, act, Y, ldy);
-        } else {
-            dim3 grid(gx, (C + 127) / 128);
-            spmm_gather_vec<1, 8><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                    X, C, ldx, bias, act, Y, ldy);
-        }
+        const int nv = gather_nv(e->n, C);
+        const uint32_t panels = (C + 128 * nv - 1) / (128 * nv);
+        const uint32_t wpb = gather_wpb(e, panels);
+        dim3 grid((e->m + wpb - 1) / wpb, panels);
+        if (nv == 2)
+            spmm_gather_vec<2, 4><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                           X, C, ldx, bias, act, Y, ldy);
+        else
+            spmm_gather_vec<1, 8><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                           X, C, ldx, bias, act, Y, ldy);
         SPX_LAUNCH_CHECK("spmm_gather_vec");
     } else {
-        if (C > 32) {
-            dim3 grid(gx, (C + 63) / 64);
-            spmm_gather_scalar<2><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                    X, C, ldx, bias, act, Y, ldy);
-        } else {
-            dim3 grid(gx, 1);
-            spmm_gather_scalar<1><<<grid, kGatherWarps * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                    X, C, ldx, bias, act, Y, ldy);
-        }
+        const int nv = C > 32 ? 2 : 1;
+        const uint32_t panels = (C + 32 * nv - 1) / (32 * nv);
+        const uint32_t wpb = gather_wpb(e, panels);
+        dim3 grid((e->m + wpb - 1) / wpb, panels);
+        if (nv == 2)
+            spmm_gather_scalar<2><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                           X, C, ldx, bias, act, Y, ldy);
+        else
+            spmm_gather_scalar<1><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                           X, C, ldx, bias, act, Y, ldy);
         SPX_LAUNCH_CHECK("spmm_gather_scalar");
     }
     return SPX_OK;
