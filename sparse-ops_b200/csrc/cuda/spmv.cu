@@ -25,7 +25,8 @@ __device__ __forceinline__ float group_sum(float v) {
 template <int LPR, bool SMEM>
 __global__ void __launch_bounds__(1024)
 spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
-                const uint32_t* __restrict__ nnz, uint32_t m, uint32_t n, uint32_t pitch,
+                const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                uint32_t m, uint32_t n, uint32_t pitch,
                 const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y)
 {
     extern __shared__ __align__(16) float xs[];
@@ -48,34 +49,38 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     const uint32_t iters = (m + stride - 1) / stride;
 
     for (uint32_t it = 0; it < iters; ++it) {
-        const uint32_t row = group + it * stride;
-        const bool live = row < m;
+        // slots of the sorted row schedule are dealt round-robin: every group gets long and short rows
+        const uint32_t slot = group + it * stride;
+        const bool live = slot < m;
+        const uint32_t row = live ? __ldg(row_order + slot) : 0u;
         const uint32_t nn = live ? __ldg(nnz + row) : 0u;
         const float4* __restrict__ w4 = reinterpret_cast<const float4*>(Wd + (size_t)row * pitch);
         const uint4* __restrict__ k4 = reinterpret_cast<const uint4*>(idx + (size_t)row * pitch);
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        // entry index of this lane's first float4
-        for (uint32_t j = lane * 4; j < nn; j += LPR * 8) {
-            const uint32_t j2 = j + LPR * 4;
-            const bool second = j2 < nn;
-            const float4 wa = __ldcs(w4 + (j >> 2));
-            const uint4 ka = __ldcs(k4 + (j >> 2));
-            float4 wb = make_float4(0.f, 0.f, 0.f, 0.f);
-            uint4 kb = make_uint4(0u, 0u, 0u, 0u);
-            if (second) {
-                wb = __ldcs(w4 + (j2 >> 2));
-                kb = __ldcs(k4 + (j2 >> 2));
+        // UNR 16-byte vectors of Wd and of idx in flight per lane; entries >= nn are padding and
+        // are neither loaded nor multiplied
+        constexpr int UNR = 4;
+        for (uint32_t j = lane * 4; j < nn; j += LPR * 4 * UNR) {
+            float4 wv[UNR];
+            uint4 kv[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const uint32_t ju = j + u * LPR * 4;
+                if (ju < nn) {
+                    wv[u] = __ldcs(w4 + (ju >> 2));
+                    kv[u] = __ldcs(k4 + (ju >> 2));
+                } else {
+                    wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    kv[u] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
-            // first vector: entries j .. j+3 (those >= nn are padding and are skipped)
-            a0 = fmaf(wa.x, xsrc[ka.x], a0);
-            if (j + 1 < nn) a1 = fmaf(wa.y, xsrc[ka.y], a1);
-            if (j + 2 < nn) a2 = fmaf(wa.z, xsrc[ka.z], a2);
-            if (j + 3 < nn) a3 = fmaf(wa.w, xsrc[ka.w], a3);
-            if (second) {
-                a0 = fmaf(wb.x, xsrc[kb.x], a0);
-                if (j2 + 1 < nn) a1 = fmaf(wb.y, xsrc[kb.y], a1);
-                if (j2 + 2 < nn) a2 = fmaf(wb.z, xsrc[kb.z], a2);
-                if (j2 + 3 < nn) a3 = fmaf(wb.w, xsrc[kb.w], a3);
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const uint32_t ju = j + u * LPR * 4;
+                if (ju < nn) a0 = fmaf(wv[u].x, xsrc[kv[u].x], a0);
+                if (ju + 1 < nn) a1 = fmaf(wv[u].y, xsrc[kv[u].y], a1);
+                if (ju + 2 < nn) a2 = fmaf(wv[u].z, xsrc[kv[u].z], a2);
+                if (ju + 3 < nn) a3 = fmaf(wv[u].w, xsrc[kv[u].w], a3);
             }
         }
         float acc = (a0 + a1) + (a2 + a3);
@@ -93,9 +98,19 @@ int launch_one(const spx_ell* e, const float* x, const float* bias, float* y, cu
         cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return spx::fail(SPX_ERR_CUDA, "spmv: shared memory opt-in failed: %s", cudaGetErrorString(err));
     }
-    kfn<<<blocks, threads, smem, s>>>(e->Wd, e->idx, e->nnz, e->m, e->n, e->pitch, x, bias, y);
+    kfn<<<blocks, threads, smem, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->n, e->pitch, x, bias, y);
     SPX_LAUNCH_CHECK("spmv_ell_kernel");
     return SPX_OK;
+}
+
+// Shrinks a persistent grid so that every group runs the same number of row iterations
+// (a grid of 9324 groups over 16384 rows would give some groups two rows and others one).
+static int balanced_blocks(uint64_t rows, int groups_per_block, int max_blocks)
+{
+    const uint64_t cap = (uint64_t)max_blocks * groups_per_block;
+    const uint64_t iters = (rows + cap - 1) / cap;
+    const uint64_t blocks = (rows + iters * groups_per_block - 1) / (iters * groups_per_block);
+    return (int)(blocks ? blocks : 1);
 }
 
 template <int LPR>
@@ -112,15 +127,12 @@ int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cu
         if (per_sm > 4) per_sm = 4;
         int threads = 2048 / per_sm;
         if (threads > 1024) threads = 1024;
-        int blocks = sms * per_sm;
-        const uint64_t max_useful = (groups_needed * LPR + threads - 1) / threads;
-        if ((uint64_t)blocks > max_useful) blocks = (int)(max_useful ? max_useful : 1);
+        threads &= ~31;
+        const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * per_sm);
         return launch_one<LPR, true>(e, x, bias, y, s, threads, blocks, xbytes);
     }
     int threads = 512;
-    int blocks = sms * 4;
-    const uint64_t max_useful = (groups_needed * LPR + threads - 1) / threads;
-    if ((uint64_t)blocks > max_useful) blocks = (int)(max_useful ? max_useful : 1);
+    const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * 4);
     return launch_one<LPR, false>(e, x, bias, y, s, threads, blocks, 0);
 }
 
