@@ -81,8 +81,9 @@ PYBIND11_MODULE(sparseops_backend, m)
             return a;
         })
         .def_property_readonly("nnz_total", &Ellpack::nnz_total)
-        .def("shard_rows", [](const Ellpack& E, uint32_t g, uint32_t G) { return E.shard_rows(g, G); },
-             py::arg("index"), py::arg("count"), "Rows of shard `index` of `count` as an independent, uploaded Ellpack");
+        .def("shard_rows", [](const Ellpack& E, uint32_t g, uint32_t G, bool upload) { return E.shard_rows(g, G, upload); },
+             py::arg("index"), py::arg("count"), py::arg("upload") = true,
+             "Rows [index*ceil(m/count), ...) as an independent Ellpack (uploaded unless upload=False)");
 
     m.def("convert_to_ellpack", &convert_to_ellpack_py, "Convert dense NumPy matrix -> ELLPACK handle (device-resident)");
     m.def("decode_from_ellpack", &decode_from_ellpack_py, "Convert ELLPACK handle -> dense NumPy matrix");

@@ -58,7 +58,7 @@ uint64_t Ellpack::nnz_total() const
     return t;
 }
 
-Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G) const
+Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G, bool do_upload) const
 {
     if (G == 0 || g >= G) throw std::runtime_error("shard_rows: bad shard index");
     const uint32_t per = (m + G - 1) / G;
@@ -69,7 +69,7 @@ Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G) const
         std::memcpy(S.idx.data(), idx.data() + size_t(lo) * r, size_t(S.m) * r * sizeof(uint32_t));
     }
     std::copy(nnz.begin() + lo, nnz.begin() + hi, S.nnz.begin());
-    S.upload();
+    if (do_upload) S.upload();
     return S;
 }
 

@@ -68,8 +68,9 @@ struct Ellpack {
     /// x[idx] for all m*r slots: what the reference leaves in Xt after a matvec
     /// (src/ellpack_matvec.cpp:48-52); zeros before the first matvec.
     std::vector<float> gathered_x() const;
-    /// Rows [g*ceil(m/G), ...) as an independent matrix (uploaded), for row-sharded runs.
-    Ellpack shard_rows(uint32_t g, uint32_t G) const;
+    /// Rows [g*ceil(m/G), (g+1)*ceil(m/G)) clipped to m, as an independent matrix, for row-sharded
+    /// runs (uploaded unless upload == false).  Every shard keeps the parent's r.
+    Ellpack shard_rows(uint32_t g, uint32_t G, bool upload = true) const;
     uint64_t nnz_total() const;
 };
 

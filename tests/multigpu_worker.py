@@ -1,0 +1,109 @@
+"""Worker of tests/test_multigpu.py: one process per GPU (torchrun), NCCL.  Exits non-zero on any
+mismatch.  Checks, against the CPU oracle on the same seeded inputs:
+  1. row-sharded SpMM with the library's own in-place all-gather (spx_allgather_rows);
+  2. SparseOnnxModel in row-sharded (tensor-parallel) mode: every layer ends with an all-gather;
+  3. SparseOnnxModel batch-sharded: each rank runs its own batch columns, no collective."""
+import ctypes as C
+import os
+import sys
+import tempfile
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "sparse-ops_b200")):
+    sys.path.insert(0, p)
+
+import onnx_wire  # noqa: E402
+import oracle  # noqa: E402
+import sparseops_backend as sb  # noqa: E402
+import spx_ctypes as sx  # noqa: E402
+
+
+def sparse(rng, m, n, p, scale=1.0):
+    W = (rng.standard_normal((m, n)) * scale).astype(np.float32)
+    W[rng.random((m, n)) >= p] = 0
+    return W
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    lib = sx.Lib()
+    lib.spx_set_device(local)
+    sb.set_device(local)
+    orc = oracle.Oracle()
+    rng = np.random.default_rng(1234)            # identical stream on every rank
+
+    # one NCCL communicator of the library, id made by rank 0
+    idbuf = [sb.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(idbuf, src=0)
+    comm = C.c_void_p()
+    lib.spx_comm_create(rank, world, idbuf[0], C.byref(comm))
+
+    # 1. row-sharded SpMM, m not divisible by world
+    m, n, Cc = 1003, 700, 96
+    W = sparse(rng, m, n, 0.1)
+    X = rng.uniform(-1, 1, (n, Cc)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = sb.encode_host(W)
+    S = E.shard_rows(rank, world, upload=False)
+    per = -(-m // world)
+    lo = min(m, rank * per)
+    h = lib.ell_create(S.Wd, S.idx, S.nnz, n)
+    dX = torch.from_numpy(X).to(dev)
+    dB = torch.from_numpy(b[lo:lo + S.m].copy()).to(dev)
+    dY = torch.zeros((per * world, Cc), device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    h.spmm(dX.data_ptr(), Cc, Cc, dB.data_ptr(), sx.ACT_RELU, dY[rank * per:].data_ptr(), Cc, stream)
+    lib.spx_allgather_rows(comm, dY.data_ptr(), per, Cc, stream)
+    torch.cuda.synchronize()
+    want = orc.spmm(orc.encode(W), X, b, act=1)
+    assert np.array_equal(dY.cpu().numpy()[:m].view(np.uint32), want.view(np.uint32)), "row-sharded SpMM differs"
+
+    # 2. + 3. model: 3 layers, relu/relu/none (bit-exact end to end), out features not divisible by world
+    dims, B = [64, 96, 80, 30 + world - 1], 8 * world
+    Ws = [sparse(rng, dims[i + 1], dims[i], 0.3, 0.3) for i in range(3)]
+    bs = [rng.standard_normal(dims[i + 1]).astype(np.float32) * 0.1 for i in range(3)]
+    x = rng.uniform(0, 1, (B, dims[0])).astype(np.float32)
+    x_mem = np.ascontiguousarray(x.T)
+    a = x_mem
+    for Wl, bl, act in zip(Ws, bs, (1, 1, 0)):
+        a = orc.spmm(orc.encode(Wl), a, bl, act=act)
+    f = tempfile.NamedTemporaryFile(suffix=f".r{rank}.onnx", delete=False)
+    f.write(onnx_wire.mlp_model(Ws, bs, ["Relu", "Relu", None], B))
+    f.close()
+    tp = sb.SparseOnnxModel(f.name)
+    tp.shard_rows(rank, world, idbuf2(rank, sb))
+    y = tp.run(x_mem.reshape(B, -1)).ravel().reshape(-1, B)
+    assert np.array_equal(y.view(np.uint32), a.view(np.uint32)), "row-sharded model differs"
+    y2 = tp.run(x_mem.reshape(B, -1)).ravel().reshape(-1, B)          # second run: graph replay
+    assert np.array_equal(y2.view(np.uint32), a.view(np.uint32)), "row-sharded model differs on replay"
+
+    bsd = sb.SparseOnnxModel(f.name)
+    os.unlink(f.name)
+    Bl = B // world
+    xl = np.ascontiguousarray(x_mem[:, rank * Bl:(rank + 1) * Bl])
+    yl = bsd.run(xl.reshape(Bl, -1)).ravel().reshape(-1, Bl)
+    assert np.array_equal(yl.view(np.uint32), a[:, rank * Bl:(rank + 1) * Bl].view(np.uint32)), "batch-sharded model differs"
+
+    lib.spx_comm_destroy(comm)
+    dist.barrier()
+    if rank == 0:
+        print(f"multigpu ok: world {world}")
+    dist.destroy_process_group()
+
+
+def idbuf2(rank, sb_mod):
+    """A second communicator id (the model owns its communicator)."""
+    buf = [sb_mod.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(buf, src=0)
+    return buf[0]
+
+
+if __name__ == "__main__":
+    main()
