@@ -59,6 +59,7 @@ def parse_args():
     ap.add_argument("--cols", type=int, default=0, help="cfg5_spmm: override C, the dense column count")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-also", action="store_true", help="skip the other configurations in the default run")
     return ap.parse_args()
 
 
@@ -369,7 +370,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": reps,
         "warmup": max(1, min(args.warmup, 2)), "ms_per_step": sec_full * 1e3, "higher_is_better": True,
-        "scaling": "strong" if wk["kind"] in ("spmm", "spmv") else "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": args.workload, "desc": wk["desc"]},
         "gflops": job_flops / sec_full / 1e9,
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind,
@@ -380,27 +381,40 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------------
-def run_ours(args):
+class Ctx:
+    """Process-wide state of the product arm: device, library handle, rank layout."""
+
+
+def setup_ours(args):
     import torch
     import torch.distributed as dist
 
     import spx_ctypes as sx
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus and world > 1:
-        args.gpus = world
+    c = Ctx()
+    c.torch, c.dist, c.sx = torch, dist, sx
+    c.world = int(os.environ.get("WORLD_SIZE", "1"))
+    c.rank = int(os.environ.get("RANK", "0"))
+    c.local = int(os.environ.get("LOCAL_RANK", "0"))
+    if c.world != args.gpus and c.world > 1:
+        args.gpus = c.world
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
+    torch.cuda.set_device(c.local)
+    c.dev = torch.device("cuda", c.local)
+    if c.world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    lib = sx.Lib()
-    lib.spx_set_device(local)
-    stream = torch.cuda.current_stream().cuda_stream
+        dist.init_process_group("nccl", device_id=c.dev)
+    c.lib = sx.Lib()
+    c.lib.spx_set_device(c.local)
+    c.stream = torch.cuda.current_stream().cuda_stream
+    return c
+
+
+def measure(args, c):
+    """Runs one workload; returns the JSON line as a dict on rank 0 (None elsewhere)."""
+    torch, dist, sx = c.torch, c.dist, c.sx
+    world, rank, local, dev, lib, stream = c.world, c.rank, c.local, c.dev, c.lib, c.stream
 
     wk = build_workload(args, rank, world)
     kind = wk["kind"]
@@ -481,11 +495,13 @@ def run_ours(args):
             xl = np.ascontiguousarray(x_mem[:, rank * Bl:(rank + 1) * Bl])
             rows_pad = model.out_features
         model.resize_buffers(Bl)
+        # operands resident in the model's own device buffers; one step = one replay of the captured loop
         dX = torch.from_numpy(xl).to(dev)
-        dY = torch.empty((rows_pad, Bl), device=dev, dtype=torch.float32)
+        lib.spx_memcpy_d2d(model.device_input_ptr(), dX.data_ptr(), dX.numel() * 4, stream)
+        torch.cuda.synchronize()
 
         def step():
-            model.run_device(dX.data_ptr(), Bl, dY.data_ptr(), stream)
+            model.run_resident(stream)
         hX = torch.from_numpy(xl).pin_memory()
         h2d, d2h = hX.numel() * 4, model.out_features * Bl * 4
 
@@ -607,7 +623,7 @@ def run_ours(args):
         line = {
             "metric": metric, "value": to_value(wk, job_bytes, sec), "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong" if kind in ("spmm", "spmv") else "weak", "vs_baseline": None, "dtype": "f32",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": args.workload, "desc": wk["desc"],
                        "l2": "flushed between timed iterations (512 MiB write)" if need_flush else "inputs larger than L2",
@@ -635,10 +651,41 @@ def run_ours(args):
                                         "gflops": job_flops / csec / 1e9}
             except Exception as ex:  # the CPU leg must never take the GPU line down
                 line["cpu_baseline"] = {"value": None, "error": repr(ex)}
+        return line
+    return None
+
+
+ALSO = [("cfg1_spmm", {}), ("cfg1_spmv", {}), ("cfg2_spmv", {"size": 16384, "sparsity": 0.90}),
+        ("cfg3_mlp", {}), ("cfg4_conv", {})]
+
+
+def run_ours(args):
+    c = setup_ours(args)
+    line = measure(args, c)
+    # The metric names SpMM, SpMV and the sparse MLP; the headline line carries the largest SpMM
+    # configuration, the other configurations ride along in "also" (device-resident timing only).
+    if c.rank == 0 and c.world == 1 and not args.no_also and args.workload == "cfg5_spmm" and args.scale == 1.0 \
+            and not args.rows and not args.cols:
+        import copy
+        also = {}
+        for name, over in ALSO:
+            a2 = copy.copy(args)
+            a2.workload, a2.no_e2e, a2.no_cpu, a2.steps = name, True, True, max(args.steps, 20)
+            for k, v in over.items():
+                setattr(a2, k, v)
+            try:
+                l2 = measure(a2, c)
+                also[name] = {"desc": l2["config"]["desc"], "metric": l2["metric"], "value": l2["value"], "unit": l2["unit"],
+                              "ms_per_step": l2["ms_per_step"], "gflops": l2["gflops"],
+                              "hbm_frac": l2["roofline"]["frac"], "l2": l2["config"]["l2"]}
+            except Exception as ex:
+                also[name] = {"error": repr(ex)}
+        line["also"] = also
+    if c.rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    if c.world > 1:
+        c.dist.barrier()
+        c.dist.destroy_process_group()
 
 
 def main():

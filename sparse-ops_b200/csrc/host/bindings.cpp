@@ -214,6 +214,10 @@ PYBIND11_MODULE(sparseops_backend, m)
         .def("run_device", [](const SparseOnnxModel& model, uintptr_t x, uint32_t B, uintptr_t y, uintptr_t stream) {
             model.run_device(reinterpret_cast<const float*>(x), B, reinterpret_cast<float*>(y), reinterpret_cast<void*>(stream));
         }, py::arg("x"), py::arg("batch"), py::arg("y"), py::arg("stream") = 0)
+        .def("device_input_ptr", [](const SparseOnnxModel& m_) { return reinterpret_cast<uintptr_t>(m_.device_input()); })
+        .def("device_output_ptr", [](const SparseOnnxModel& m_) { return reinterpret_cast<uintptr_t>(m_.device_output()); })
+        .def("run_resident", [](const SparseOnnxModel& m_, uintptr_t stream) { m_.run_resident(reinterpret_cast<void*>(stream)); },
+             py::arg("stream") = 0, "Replay the captured layer loop on the model's own device buffers (asynchronous)")
         .def("shard_rows", [](SparseOnnxModel& model, int rank, int world, py::bytes id) {
             std::string s = id;
             if (world > 1 && s.size() != SPX_UNIQUE_ID_BYTES) throw std::runtime_error("unique id must be 128 bytes");

@@ -397,6 +397,25 @@ void SparseOnnxModel::run(const float* input, uint32_t B, float* output) const
     check(spx_stream_sync(ex.stream), "run");
 }
 
+float* SparseOnnxModel::device_input() const
+{
+    if (!exec_) throw std::runtime_error("device_input: call resize_buffers(B) first");
+    return exec_->buf.at(input_name_);
+}
+
+float* SparseOnnxModel::device_output() const
+{
+    if (!exec_) throw std::runtime_error("device_output: call resize_buffers(B) first");
+    return exec_->buf.at(output_name_);
+}
+
+void SparseOnnxModel::run_resident(void* stream) const
+{
+    if (!exec_) throw std::runtime_error("run_resident: call resize_buffers(B) first");
+    if (exec_->graph) check(spx_graph_launch(exec_->graph, stream), "graph launch");
+    else launch_layers(device_input(), device_output(), exec_->B, stream);
+}
+
 void SparseOnnxModel::run_device(const float* d_input, uint32_t B, float* d_output, void* stream) const
 {
     if (!exec_ || exec_->B != B) build_exec(B);

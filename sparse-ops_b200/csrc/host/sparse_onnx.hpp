@@ -52,6 +52,13 @@ public:
     void run(const float* input, uint32_t B, float* output) const;
     /// Device buffers in and out; launches the layer loop on `stream` without synchronising.
     void run_device(const float* d_input, uint32_t B, float* d_output, void* stream) const;
+    /// The model's own device buffers for the current batch (valid after resize_buffers / run):
+    /// fill device_input(), call run_resident(), read device_output().  run_resident replays the
+    /// captured CUDA graph on `stream` (or launches the layers when no graph was captured) and does
+    /// not synchronise.
+    float* device_input() const;
+    float* device_output() const;
+    void run_resident(void* stream) const;
     /// Output dims as labelled in the ONNX graph (static shape recorded at load).
     std::vector<size_t> output_shape() const;
     /// (Re)allocate the activation buffers for batch B and capture the layer loop as a CUDA graph.

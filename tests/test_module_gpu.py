@@ -157,6 +157,18 @@ def test_model_resize_and_device_run(backend, golden, orc, cuda):
     m.run_device(dX.data_ptr(), 5, dY.data_ptr(), torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert_bit_equal(dY.cpu().numpy(), want, "device run")
+    # resident replay of the captured loop on the model's own buffers
+    m.resize_buffers(5)
+    dX2 = torch.from_numpy(x_mem).to(cuda)
+    n_in = dX2.numel() * 4
+    import spx_ctypes as sx
+    sx.Lib().spx_memcpy_d2d(m.device_input_ptr(), dX2.data_ptr(), n_in, 0)
+    torch.cuda.synchronize()
+    m.run_resident(0)
+    out = torch.empty(want.shape, device=cuda)
+    sx.Lib().spx_memcpy_d2d(out.data_ptr(), m.device_output_ptr(), out.numel() * 4, 0)
+    torch.cuda.synchronize()
+    assert_bit_equal(out.cpu().numpy(), want, "resident run")
 
 
 def test_model_scaled_config3_vs_oracle(backend, orc, cuda):
