@@ -37,7 +37,7 @@ __device__ __forceinline__ void fma4(float4& a, float w, const float4& x) {
 // spmm_gather<NV>: lane owns NV float4 groups: columns c0 + v*128 + 4*lane .. +3.
 // ---------------------------------------------------------------------------------------
 template <int NV, int G>
-__global__ void __launch_bounds__(kGatherWarps * 32)
+__global__ void __launch_bounds__(kGatherWarps * 32, 4)
 spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
                 uint32_t m, uint32_t pitch,
