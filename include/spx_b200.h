@@ -153,6 +153,16 @@ int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int layout, cons
  * out may alias a. */
 int spx_eltwise(int op, const float* a, const float* b, float* out, uint64_t count, void* stream);
 
+/* MaxPool on a [C,H,W,B] tensor: max over the in-image taps of each window, -inf when a window
+ * lies entirely in the padding.  Ho = (H + pH0 + pH1 - kH)/sH + 1 (likewise Wo); out is
+ * [C,Ho,Wo,B].  Replaces applyMaxPool (src/layers/pool.cpp:28-104). */
+int spx_maxpool2d(const float* in, uint32_t C, uint32_t H, uint32_t W, uint32_t B, uint32_t kH, uint32_t kW,
+                  uint32_t sH, uint32_t sW, uint32_t pH0, uint32_t pW0, uint32_t pH1, uint32_t pW1, float* out,
+                  void* stream);
+/* Mean over H*W of a [C,H,W,B] tensor into [C,B]: sequential sum in storage order times
+ * 1.0f/(H*W).  Replaces applyGlobalAveragePool (src/layers/pool.cpp:106-154). */
+int spx_global_avgpool(const float* in, uint32_t C, uint32_t H, uint32_t W, uint32_t B, float* out, void* stream);
+
 /* ---- the same calls on HOST buffers (what the reference's Python binding does) ---------- */
 /* X, bias, Y are host arrays; copies in and out go through pinned staging owned by the
  * handle's device context.  Replaces the ellpack_matmul / ellpack_matvec lambdas of

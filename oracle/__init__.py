@@ -89,6 +89,8 @@ class Oracle:
                                C.c_size_t, _f32p, C.c_int, _f32p, C.c_size_t]
         L.orc_spmv.argtypes = [C.c_uint32, C.c_uint32, _f32p, _u32p, _u32p, _f32p, _f32p, _f32p]
         L.orc_spmv_absbound.argtypes = [C.c_uint32, C.c_uint32, _f32p, _u32p, _u32p, _f32p, _f32p, _f64p]
+        L.orc_maxpool_pf.argtypes = [_f32p] + [C.c_uint32] * 12 + [_f32p]
+        L.orc_gap_pf.argtypes = [_f32p] + [C.c_uint32] * 4 + [_f32p]
         L.orc_conv2d.argtypes = [C.c_uint32, C.c_uint32, _f32p, _u32p, _u32p] + [C.c_uint32] * 13 + \
                                 [C.c_int, _f32p, C.c_uint32, _f32p, C.c_int, _f32p]
 
@@ -145,6 +147,23 @@ class Oracle:
                             g["sH"], g["sW"], g["pH"], g["pW"], g["dH"], g["dW"], g["H"], g["W"],
                             Ho, Wo, layout, _fp(src), B, _fp(bias), act, _fp(dst))
         return dst
+
+    def maxpool_pf(self, x, k, s, pad):
+        """x: [C,H,W,B]; k, s: (h, w); pad: (h0, w0, h1, w1)."""
+        x = _f32(x)
+        Cc, H, W, B = x.shape
+        Ho = (H + pad[0] + pad[2] - k[0]) // s[0] + 1
+        Wo = (W + pad[1] + pad[3] - k[1]) // s[1] + 1
+        out = np.empty((Cc, Ho, Wo, B), dtype=np.float32)
+        self.lib.orc_maxpool_pf(_fp(x), Cc, H, W, B, k[0], k[1], s[0], s[1], pad[0], pad[1], pad[2], pad[3], _fp(out))
+        return out
+
+    def gap_pf(self, x):
+        x = _f32(x)
+        Cc, H, W, B = x.shape
+        out = np.empty((Cc, B), dtype=np.float32)
+        self.lib.orc_gap_pf(_fp(x), Cc, H, W, B, _fp(out))
+        return out
 
     def activation(self, x, act: int):
         x = _f32(x)

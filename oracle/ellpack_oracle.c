@@ -232,3 +232,46 @@ void orc_conv2d(uint32_t Cout, uint32_t r, const float* Wd, const uint32_t* idx,
         }
     }
 }
+
+/* ------------------------------------------------------------------------
+ * Pools on [C,H,W,B] tensors.  Arithmetic of the reference's applyMaxPool
+ * (src/layers/pool.cpp:28-104: max over in-image taps from -inf) and
+ * applyGlobalAveragePool (:106-154: sum over h then w from 0, times
+ * 1.0f/(H*W)).  The reference indexes them as b + B*(c + C*(h + H*w)); the
+ * per-(c,b) order of operations is the same, so on the same logical tensor
+ * the results are bit-identical.
+ * ---------------------------------------------------------------------- */
+void orc_maxpool_pf(const float* in, uint32_t C, uint32_t H, uint32_t W, uint32_t B,
+                    uint32_t kH, uint32_t kW, uint32_t sH, uint32_t sW,
+                    uint32_t pH0, uint32_t pW0, uint32_t pH1, uint32_t pW1, float* out)
+{
+    const uint32_t Ho = (H + pH0 + pH1 - kH) / sH + 1, Wo = (W + pW0 + pW1 - kW) / sW + 1;
+    for (uint32_t c = 0; c < C; ++c)
+        for (uint32_t oh = 0; oh < Ho; ++oh)
+            for (uint32_t ow = 0; ow < Wo; ++ow)
+                for (uint32_t b = 0; b < B; ++b) {
+                    float v = -INFINITY;
+                    for (uint32_t kh = 0; kh < kH; ++kh) {
+                        const int ih = (int)(oh * sH) - (int)pH0 + (int)kh;
+                        if ((unsigned)ih >= H) continue;
+                        for (uint32_t kw = 0; kw < kW; ++kw) {
+                            const int iw = (int)(ow * sW) - (int)pW0 + (int)kw;
+                            if ((unsigned)iw >= W) continue;
+                            const float x = in[(((size_t)c * H + ih) * W + iw) * B + b];
+                            v = x > v ? x : v;
+                        }
+                    }
+                    out[(((size_t)c * Ho + oh) * Wo + ow) * B + b] = v;
+                }
+}
+
+void orc_gap_pf(const float* in, uint32_t C, uint32_t H, uint32_t W, uint32_t B, float* out)
+{
+    const float scale = 1.0f / (float)(H * W);
+    for (uint32_t c = 0; c < C; ++c)
+        for (uint32_t b = 0; b < B; ++b) {
+            float s = 0.0f;
+            for (uint32_t i = 0; i < H * W; ++i) s += in[((size_t)c * H * W + i) * B + b];
+            out[(size_t)c * B + b] = s * scale;
+        }
+}

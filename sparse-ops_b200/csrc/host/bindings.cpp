@@ -230,7 +230,7 @@ PYBIND11_MODULE(sparseops_backend, m)
         .def("flops_per_run", &SparseOnnxModel::flops_per_run, py::arg("batch"))
         .def("layer_summary", [](const SparseOnnxModel& model) {
             py::list out;
-            static const char* names[] = { "MatMul", "Relu", "Sigmoid", "Tanh", "Add", "Conv" };
+            static const char* names[] = { "MatMul", "Relu", "Sigmoid", "Tanh", "Add", "Conv", "MaxPool", "GlobalAveragePool" };
             for (size_t i = 0; i < model.num_layers(); ++i) {
                 const spx::Layer& L = model.layer(i);
                 py::dict d;

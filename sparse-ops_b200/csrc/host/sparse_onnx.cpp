@@ -188,6 +188,54 @@ SparseOnnxModel::SparseOnnxModel(const std::string& onnx_path, bool upload_weigh
             continue;
         }
 
+        if (op == "MaxPool" || op == "GlobalAveragePool") {     // attributes as the reference reads them (:304-350)
+            const std::string x_name = resolve(node.inputs.at(0));
+            const auto in_shape = shape_map_.at(x_name);
+            if (in_shape.size() != 4) throw std::runtime_error("Pool input must be 4D");
+            Layer L;
+            PoolGeom& g = L.pool;
+            g.C = uint32_t(in_shape[1]); g.H = uint32_t(in_shape[2]); g.W = uint32_t(in_shape[3]);
+            if (op == "GlobalAveragePool") {
+                L.op = LayerOp::GlobalAveragePool;
+                L.out_features = g.C;
+                shape_map_[out] = { in_shape[0], int(g.C) };
+            } else {
+                L.op = LayerOp::MaxPool;
+                for (const auto& a : node.attributes) {
+                    if (a.name == "kernel_shape" && a.ints.size() == 2) { g.kH = uint32_t(a.ints[0]); g.kW = uint32_t(a.ints[1]); }
+                    else if (a.name == "strides" && a.ints.size() == 2) { g.sH = uint32_t(a.ints[0]); g.sW = uint32_t(a.ints[1]); }
+                    else if (a.name == "pads" && a.ints.size() == 4) {
+                        g.pH0 = uint32_t(a.ints[0]); g.pW0 = uint32_t(a.ints[1]);
+                        g.pH1 = uint32_t(a.ints[2]); g.pW1 = uint32_t(a.ints[3]);
+                    }
+                }
+                if (g.kH == 0 || g.kW == 0 || g.sH == 0 || g.sW == 0 || g.H + g.pH0 + g.pH1 < g.kH || g.W + g.pW0 + g.pW1 < g.kW)
+                    throw std::runtime_error("MaxPool: bad kernel / stride / padding");
+                g.Ho = (g.H + g.pH0 + g.pH1 - g.kH) / g.sH + 1;
+                g.Wo = (g.W + g.pW0 + g.pW1 - g.kW) / g.sW + 1;
+                L.out_features = uint64_t(g.C) * g.Ho * g.Wo;
+                shape_map_[out] = { in_shape[0], int(g.C), int(g.Ho), int(g.Wo) };
+            }
+            L.inputs = { x_name };
+            L.outputs = { out };
+            layers_.push_back(std::move(L));
+            continue;
+        }
+
+        if (op == "Flatten") {                    // [C,H,W,B] is already [features x B]: alias (:353-378)
+            int64_t axis = 1;
+            if (const auto* a = node.find("axis")) axis = a->i;
+            const std::string in = resolve(node.inputs.at(0));
+            const auto in_shape = shape_map_.at(in);
+            if (axis != 1) throw std::runtime_error("Flatten: only axis=1 is supported");
+            int prod = 1;
+            for (size_t d = 1; d < in_shape.size(); ++d) prod *= in_shape[d];
+            name_alias_[out] = in;
+            shape_map_[out] = { in_shape[0], prod };
+            flat_shape_[in] = shape_map_[out];
+            continue;
+        }
+
         if (op == "Identity") {                   // alias, no layer (:522-534)
             const std::string in = resolve(node.inputs.at(0));
             name_alias_[out] = in;
@@ -198,7 +246,9 @@ SparseOnnxModel::SparseOnnxModel(const std::string& onnx_path, bool upload_weigh
 
         throw std::runtime_error("Unsupported ONNX op: " + op);
     }
+    const std::string labelled_output = graph.outputs[0].name;
     output_name_ = resolve(output_name_);
+    if (shape_map_.count(labelled_output)) output_label_shape_ = shape_map_.at(labelled_output);
 
     // Fuse an activation that directly follows a MatMul / Conv and is its only consumer
     // (reference: Relu only, src/sparse_onnx.cpp:573-620).
@@ -230,7 +280,7 @@ SparseOnnxModel::SparseOnnxModel(const std::string& onnx_path, bool upload_weigh
 std::vector<size_t> SparseOnnxModel::output_shape() const
 {
     std::vector<size_t> dims;
-    for (int d : shape_map_.at(output_name_)) dims.push_back(size_t(d));
+    for (int d : output_label_shape_.empty() ? shape_map_.at(output_name_) : output_label_shape_) dims.push_back(size_t(d));
     return dims;
 }
 
@@ -303,6 +353,8 @@ void SparseOnnxModel::build_exec(uint32_t B) const
             const uint64_t per_row = L.op == LayerOp::Conv ? uint64_t(L.geom.Ho) * L.geom.Wo : 1;
             const uint64_t m = L.E->m;
             padded = world_ > 1 ? ((m + world_ - 1) / world_) * world_ * per_row : rows;
+        } else if (L.op == LayerOp::MaxPool || L.op == LayerOp::GlobalAveragePool) {
+            rows = padded = L.out_features;
         } else {
             rows = padded = ex->rows.at(L.inputs[0]);
         }
@@ -368,6 +420,17 @@ void SparseOnnxModel::launch_layers(const float* d_in, float* d_out, uint32_t B,
         case LayerOp::Tanh: {
             const int op = L.op == LayerOp::Relu ? SPX_OP_RELU : L.op == LayerOp::Sigmoid ? SPX_OP_SIGMOID : SPX_OP_TANH;
             check(spx_eltwise(op, src, nullptr, dst, ex.rows.at(L.inputs[0]) * B, stream), "activation layer");
+            break;
+        }
+        case LayerOp::MaxPool: {
+            const PoolGeom& g = L.pool;
+            check(spx_maxpool2d(src, g.C, g.H, g.W, B, g.kH, g.kW, g.sH, g.sW, g.pH0, g.pW0, g.pH1, g.pW1, dst, stream),
+                  "MaxPool layer");
+            break;
+        }
+        case LayerOp::GlobalAveragePool: {
+            const PoolGeom& g = L.pool;
+            check(spx_global_avgpool(src, g.C, g.H, g.W, B, dst, stream), "GlobalAveragePool layer");
             break;
         }
         case LayerOp::Add: {

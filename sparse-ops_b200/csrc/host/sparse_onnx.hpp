@@ -8,6 +8,12 @@
 // into one device array, MatMul/Conv + Relu pairs are fused (:573-620; Sigmoid and Tanh are
 // fused into the producing kernel's epilogue as well -- same values, one pass less).
 //
+// Beyond the reference: MaxPool, GlobalAveragePool and Flatten also work on [C,H,W,B] tensors
+// (the reference indexes those three in an older layout that its own convolution no longer
+// produces, so conv -> pool / flatten graphs are wrong there).  In [C,H,W,B] a Flatten is a pure
+// alias whose feature order (c, h, w) equals the flatten order of an NCHW tensor, so fully
+// connected weights need no column permutation.
+//
 // Memory contract of run(), identical to the reference (src/model_run.cpp, src/layers/matmul.cpp:
 // activations are feature-major): the input bytes are read as [in_features x B] for dense
 // models or [Cin, H, W, B] for convolutional ones, B fastest; the output bytes are [M x B] /
@@ -24,7 +30,15 @@
 
 namespace spx {
 
-enum class LayerOp { MatMul, Relu, Sigmoid, Tanh, Add, Conv };
+enum class LayerOp { MatMul, Relu, Sigmoid, Tanh, Add, Conv, MaxPool, GlobalAveragePool };
+
+/// MaxPool / GlobalAveragePool geometry (reference: PoolAttr, include/sparse_onnx.hpp:95-105).
+struct PoolGeom {
+    uint32_t C = 0, H = 0, W = 0;
+    uint32_t kH = 1, kW = 1, sH = 1, sW = 1;
+    uint32_t pH0 = 0, pW0 = 0, pH1 = 0, pW1 = 0;
+    uint32_t Ho = 1, Wo = 1;
+};
 
 struct Layer {
     LayerOp op;
@@ -34,6 +48,7 @@ struct Layer {
     size_t bias_offset = 0;            ///< into the packed device bias array
     int act = SPX_ACT_NONE;            ///< activation fused into the epilogue
     spx_conv_geom geom{};              ///< Conv only
+    PoolGeom pool{};                   ///< MaxPool / GlobalAveragePool only
     std::vector<std::string> inputs, outputs;
     uint64_t out_features = 0;         ///< output elements per batch column
 };
@@ -88,6 +103,8 @@ private:
     std::vector<int> input_shape_;
     std::unordered_map<std::string, std::vector<int>> shape_map_;
     std::unordered_map<std::string, std::string> name_alias_;
+    std::unordered_map<std::string, std::vector<int>> flat_shape_;
+    std::vector<int> output_label_shape_;
     std::string input_name_, output_name_;
     int rank_ = 0, world_ = 1;
     spx_comm* comm_ = nullptr;

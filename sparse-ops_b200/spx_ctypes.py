@@ -83,6 +83,8 @@ SIGNATURES = {
     "spx_conv2d": (C.c_int, [_vp, C.POINTER(ConvGeom), C.c_int, _vp, C.c_uint32, _vp, C.c_int, _vp, _vp]),
     "spx_conv2d_static": (C.c_int, [_vp, C.POINTER(ConvGeom), C.c_int, _vp, C.c_uint32, _vp, C.c_int, _vp, _vp]),
     "spx_eltwise": (C.c_int, [C.c_int, _vp, _vp, _vp, C.c_uint64, _vp]),
+    "spx_maxpool2d": (C.c_int, [_vp] + [C.c_uint32] * 12 + [_vp, _vp]),
+    "spx_global_avgpool": (C.c_int, [_vp] + [C.c_uint32] * 4 + [_vp, _vp]),
     "spx_spmm_host": (C.c_int, [_vp, _vp, C.c_uint32, _vp, C.c_int, _vp]),
     "spx_spmv_host": (C.c_int, [_vp, _vp, _vp, _vp]),
     "spx_comm_unique_id": (C.c_int, [C.c_char_p]),

@@ -131,6 +131,22 @@ def main():
     out["cnn_x_mem"] = np.ascontiguousarray(x.transpose(1, 2, 3, 0))    # [C,H,W,B]
     out["cnn_shape_ref"], out["cnn_y_mem_ref"] = run_model(blob, out["cnn_x_mem"], B)
 
+    # --- pools: the reference runs them only inside a model and indexes them b + B*(c + C*(h + H*w)),
+    # so the logical NCHW tensor is handed over (and read back) in that memory order ---------------
+    B, Cc, H, W_ = 3, 5, 9, 8
+    x = rng.standard_normal((B, Cc, H, W_)).astype(np.float32)
+    x_f = np.ascontiguousarray(x.transpose(3, 2, 1, 0))                   # [w][h][c][b]
+    mp = onnx_wire.model([onnx_wire.node("MaxPool", ["input"], ["y"], [
+        onnx_wire.attr_ints("kernel_shape", [3, 3]), onnx_wire.attr_ints("strides", [2, 2]),
+        onnx_wire.attr_ints("pads", [1, 1, 1, 1])])], [], ("input", (B, Cc, H, W_)), ("y", (B, Cc, 5, 4)))
+    shape, y = run_model(mp, x_f, B)
+    out["pool_x_nchw"] = x
+    out["pool_max_ref"] = np.ascontiguousarray(y.reshape(4, 5, Cc, B).transpose(3, 2, 1, 0))   # logical NCHW
+    gp = onnx_wire.model([onnx_wire.node("GlobalAveragePool", ["input"], ["y"])], [],
+                         ("input", (B, Cc, H, W_)), ("y", (B, Cc)))
+    shape, y = run_model(gp, x_f, B)
+    out["pool_gap_ref"] = np.ascontiguousarray(y[:Cc * B].reshape(Cc, B).T)                     # logical (B, C)
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1024:.0f} KiB")

@@ -164,3 +164,31 @@ def test_workload_generators_are_seeded_and_shardable():
     assert (d[mask] > 0).all()
     Wd, idx, n3 = wl.csr_to_ell(8192, rp, col, val)
     assert Wd.shape == (8192, 256) and np.array_equal(n3, nnz.astype(np.uint32))
+
+
+def test_planner_cnn_with_pools_and_flatten(backend):
+    import onnx_wire as ow
+    rng = np.random.default_rng(8)
+    w1 = rng.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    wf = rng.standard_normal((7, 4 * 4 * 4)).astype(np.float32)
+    nodes = [ow.node("Conv", ["input", "w1"], ["c1"], [ow.attr_ints("kernel_shape", [3, 3]), ow.attr_ints("pads", [1, 1, 1, 1])]),
+             ow.node("Relu", ["c1"], ["r1"]),
+             ow.node("MaxPool", ["r1"], ["p1"], [ow.attr_ints("kernel_shape", [2, 2]), ow.attr_ints("strides", [2, 2])]),
+             ow.node("Flatten", ["p1"], ["f"], [ow.attr_int("axis", 1)]),
+             ow.node("Gemm", ["f", "wf"], ["y"], [ow.attr_int("transB", 1)])]
+    path = _write(ow.model(nodes, [ow.tensor("w1", w1), ow.tensor("wf", wf)], ("input", (2, 3, 8, 8)), ("y", (2, 7))))
+    try:
+        m = backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    L = m.layer_summary()
+    assert [l["op"] for l in L] == ["Conv", "MaxPool", "MatMul"]      # Relu fused, Flatten is an alias
+    assert L[0]["act"] == 1 and L[2]["inputs"] == ["p1"] and L[2]["n"] == 64
+    assert m.output_shape() == [2, 7]
+    gap = [ow.node("GlobalAveragePool", ["input"], ["g"]), ow.node("Flatten", ["g"], ["y"])]
+    path = _write(ow.model(gap, [], ("input", (2, 3, 8, 8)), ("y", (2, 3))))
+    try:
+        m = backend.SparseOnnxModel(path, upload_weights=False)
+    finally:
+        os.unlink(path)
+    assert [l["op"] for l in m.layer_summary()] == ["GlobalAveragePool"] and m.output_shape() == [2, 3]

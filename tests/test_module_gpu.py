@@ -184,3 +184,41 @@ def test_model_scaled_config3_vs_oracle(backend, orc, cuda):
     pre = orc.spmm(orc.encode(d["weights"][3]), a, d["biases"][3])
     assert np.abs(y - orc.activation(pre, 2)).max() <= 1e-6
     assert m.flops_per_run(d["B"]) == 2.0 * d["B"] * sum(int(np.count_nonzero(W)) for W in d["weights"])
+
+
+def test_model_resnet_style_graph_vs_torch(backend, cuda):
+    """conv-relu-maxpool, a residual block (conv-relu-conv, add, relu), global average pool, flatten,
+    fully connected, sigmoid -- all in [C,H,W,B].  The reference itself is inconsistent on such graphs,
+    so the check is against a dense fp32 torch evaluation (tolerance 1e-4 like the reference's scripts)."""
+    import onnx_wire as ow
+    import torch.nn.functional as F
+    rng = np.random.default_rng(21)
+    B, Cin, Cm, H, W = 4, 3, 8, 16, 16
+
+    def sp(shape, p, scale):
+        w = (rng.standard_normal(shape) * scale).astype(np.float32)
+        w[rng.random(shape) >= p] = 0
+        return w
+    w1, b1 = sp((Cm, Cin, 3, 3), 0.5, 0.3), rng.standard_normal(Cm).astype(np.float32) * 0.1
+    w2, b2 = sp((Cm, Cm, 3, 3), 0.3, 0.2), rng.standard_normal(Cm).astype(np.float32) * 0.1
+    w3, b3 = sp((Cm, Cm, 3, 3), 0.3, 0.2), rng.standard_normal(Cm).astype(np.float32) * 0.1
+    wf, bf = sp((10, Cm), 0.6, 0.5), rng.standard_normal(10).astype(np.float32) * 0.1
+    conv = lambda i, w, b, o: ow.node("Conv", [i, w, b], [o], [ow.attr_ints("kernel_shape", [3, 3]), ow.attr_ints("pads", [1, 1, 1, 1])])
+    nodes = [conv("input", "w1", "b1", "c1"), ow.node("Relu", ["c1"], ["r1"]),
+             ow.node("MaxPool", ["r1"], ["p1"], [ow.attr_ints("kernel_shape", [3, 3]), ow.attr_ints("strides", [2, 2]), ow.attr_ints("pads", [1, 1, 1, 1])]),
+             conv("p1", "w2", "b2", "c2"), ow.node("Relu", ["c2"], ["r2"]), conv("r2", "w3", "b3", "c3"),
+             ow.node("Add", ["c3", "p1"], ["s"]), ow.node("Relu", ["s"], ["r3"]),
+             ow.node("GlobalAveragePool", ["r3"], ["g"]), ow.node("Flatten", ["g"], ["f"]),
+             ow.node("Gemm", ["f", "wf", "bf"], ["fc"], [ow.attr_int("transB", 1)]), ow.node("Sigmoid", ["fc"], ["y"])]
+    inits = [ow.tensor(n, a) for n, a in (("w1", w1), ("b1", b1), ("w2", w2), ("b2", b2), ("w3", w3), ("b3", b3), ("wf", wf), ("bf", bf))]
+    m = _load(backend, ow.model(nodes, inits, ("input", (B, Cin, H, W)), ("y", (B, 10))))
+    ops = [l["op"] for l in m.layer_summary()]
+    assert ops == ["Conv", "MaxPool", "Conv", "Conv", "Add", "Relu", "GlobalAveragePool", "MatMul"]
+    x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
+    y_mem = m.run(np.ascontiguousarray(x.transpose(1, 2, 3, 0)).reshape(B, Cin, H, W))     # [C,H,W,B] bytes
+    got = y_mem.ravel().reshape(10, B).T
+    t = torch.from_numpy
+    p1 = F.max_pool2d(F.relu(F.conv2d(t(x), t(w1), t(b1), padding=1)), 3, 2, 1)
+    r3 = F.relu(F.conv2d(F.relu(F.conv2d(p1, t(w2), t(b2), padding=1)), t(w3), t(b3), padding=1) + p1)
+    want = torch.sigmoid(F.linear(r3.mean((2, 3)), t(wf), t(bf))).numpy()
+    assert np.abs(got - want).max() <= 1e-4

@@ -74,3 +74,13 @@ def test_tolerance_bound_is_meaningful(orc, golden):
     y = orc.spmv(E, x, b)
     y64 = golden["mm_d_W"].astype(np.float64) @ x.astype(np.float64) + b
     assert (np.abs(y - y64) <= 1e-5 * orc.absbound(E, x, b)).all()
+
+
+def test_pools_match_reference(orc, golden):
+    """The reference indexes its pool layers in an older layout; on the same LOGICAL tensor the
+    [C,H,W,B] restatement gives bit-identical values."""
+    x = golden["pool_x_nchw"]
+    pf = np.ascontiguousarray(x.transpose(1, 2, 3, 0))
+    mx = orc.maxpool_pf(pf, (3, 3), (2, 2), (1, 1, 1, 1)).transpose(3, 0, 1, 2)
+    assert_bit_equal(mx, golden["pool_max_ref"], "maxpool")
+    assert_bit_equal(orc.gap_pf(pf).T, golden["pool_gap_ref"], "global average pool")

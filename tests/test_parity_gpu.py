@@ -314,3 +314,24 @@ def test_config1_scaled_and_linearity(lib, orc, cuda):
     sub = orc.encode(full["W"][:64])
     assert_bit_equal(gpu_spmm(gpu_ell(lib, sub), X1, full["bias"][:64], sx.ACT_NONE, cuda),
                      orc.spmm(sub, X1, full["bias"][:64]), "cfg1 rows 0..63")
+
+
+@pytest.mark.parametrize("B,C,H,W,k,s,pad", [(3, 5, 9, 8, 3, 2, 1), (8, 4, 12, 12, 2, 2, 0), (1, 2, 7, 5, 3, 1, 1), (16, 8, 6, 6, 3, 3, 0)])
+def test_pools_bit_exact(lib, orc, golden, cuda, B, C, H, W, k, s, pad):
+    rng = np.random.default_rng([B, C, H, W])
+    x = golden["pool_x_nchw"] if (B, C, H, W) == (3, 5, 9, 8) else rng.standard_normal((B, C, H, W)).astype(np.float32)
+    pf = np.ascontiguousarray(x.transpose(1, 2, 3, 0))
+    want = orc.maxpool_pf(pf, (k, k), (s, s), (pad, pad, pad, pad))
+    dX = dev(pf, cuda)
+    out = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
+    lib.spx_maxpool2d(dX.data_ptr(), C, H, W, B, k, k, s, s, pad, pad, pad, pad, out.data_ptr(), 0)
+    gap = torch.full((C, B), float("nan"), device=cuda, dtype=torch.float32)
+    lib.spx_global_avgpool(dX.data_ptr(), C, H, W, B, gap.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert_bit_equal(out.cpu().numpy(), want, "maxpool")
+    assert_bit_equal(gap.cpu().numpy(), orc.gap_pf(pf), "global average pool")
+    ref = torch.nn.functional.max_pool2d(torch.from_numpy(x), k, s, pad).numpy()
+    assert np.array_equal(out.cpu().numpy().transpose(3, 0, 1, 2), ref)
+    if (B, C, H, W) == (3, 5, 9, 8):        # the reference binary's own outputs on this tensor
+        assert_bit_equal(out.cpu().numpy().transpose(3, 0, 1, 2), golden["pool_max_ref"], "maxpool vs reference")
+        assert_bit_equal(gap.cpu().numpy().T, golden["pool_gap_ref"], "gap vs reference")
