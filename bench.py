@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
     ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
+    ap.add_argument("--nchw", action="store_true", help="cfg4_conv: NCHW tensors instead of [C,H,W,B]")
     ap.add_argument("--rows", type=int, default=0, help="cfg5_spmm: override the row count (profiling on a smaller case)")
     ap.add_argument("--cols", type=int, default=0, help="cfg5_spmm: override C, the dense column count")
     ap.add_argument("--no-e2e", action="store_true")
@@ -206,7 +207,7 @@ def build_workload(args, rank: int, world: int):
         return dict(kind="mlp", **d, desc=f"sparse MLP {'-'.join(map(str, d['dims']))}, 90% sparse, batch {d['B']}")
     if w == "cfg4_conv":
         d = wl.cfg4(s, layers=1)
-        return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, [C,H,W,B]")
+        return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, " + ("NCHW" if args.nchw else "[C,H,W,B]"))
     raise SystemExit(f"unknown workload {w}")
 
 
@@ -422,6 +423,7 @@ def measure(args, c):
     h2d = d2h = 0
     e2e_step = None
     ag_step = None
+    fused_step = None
 
     if kind in ("spmm", "spmv"):
         rowptr, col, val = wk["csr"]
@@ -453,6 +455,37 @@ def measure(args, c):
                 def ag_step():
                     ell.spmm(dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, Yslab.data_ptr(), C, stream)
                     dist.all_gather_into_tensor(Yfull, Yslab)
+                # the same exchange fused into the epilogue: stores into every rank's full buffer
+                # (own + peers' buffers opened over IPC), followed by a stream-ordered barrier
+                import ctypes as Ct
+                fbuf = Ct.c_void_p()
+                lib.spx_malloc(Ct.byref(fbuf), wk["m"] * C * 4)
+                hnd = Ct.create_string_buffer(sx.IPC_HANDLE_BYTES)
+                lib.spx_ipc_export(fbuf, hnd)
+                hs = [None] * world
+                dist.all_gather_object(hs, hnd.raw)
+                plist = []
+                for g_ in range(world):
+                    if g_ == rank:
+                        plist.append(fbuf.value)
+                    else:
+                        pp = Ct.c_void_p()
+                        lib.spx_ipc_open(hs[g_], Ct.byref(pp))
+                        plist.append(pp.value)
+                parr = (Ct.c_void_p * world)(*plist)
+                idb = [None]
+                if rank == 0:
+                    ub = Ct.create_string_buffer(sx.UNIQUE_ID_BYTES)
+                    lib.spx_comm_unique_id(ub)
+                    idb = [ub.raw]
+                dist.broadcast_object_list(idb, src=0)
+                fcomm = Ct.c_void_p()
+                lib.spx_comm_create(rank, world, idb[0], Ct.byref(fcomm))
+
+                def fused_step():
+                    lib.spx_spmm_bcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, parr, world,
+                                       wk["row0"], C, stream)
+                    lib.spx_comm_barrier(fcomm, stream)
             working_set = (wk["n"] * C + wk["rows"] * C) * 4 + 8 * ell.nnz_total
         else:
             dx = torch.from_numpy(wk["x"]).to(dev)
@@ -517,21 +550,24 @@ def measure(args, c):
         ell = lib.ell_create(Eh.Wd, Eh.idx, Eh.nnz, Eh.n)
         nnz_total = 0
         Bl = B // world
-        x_pf = np.ascontiguousarray(wk["x_nchw"][rank * Bl:(rank + 1) * Bl].transpose(1, 2, 3, 0))
+        layout = sx.LAYOUT_NCHW if args.nchw else sx.LAYOUT_PF
+        xs = wk["x_nchw"][rank * Bl:(rank + 1) * Bl]
+        x_in = np.ascontiguousarray(xs if args.nchw else xs.transpose(1, 2, 3, 0))
         g = sx.conv_geom(Cc, Cc, 3, 3, H, W, pH=1, pW=1)
-        dX = torch.from_numpy(x_pf).to(dev)
+        dX = torch.from_numpy(x_in).to(dev)
         dB = torch.from_numpy(wk["biases"][0]).to(dev)
-        dY = torch.empty((Cc, H, W, Bl), device=dev, dtype=torch.float32)
+        oshape = (Bl, Cc, H, W) if args.nchw else (Cc, H, W, Bl)
+        dY = torch.empty(oshape, device=dev, dtype=torch.float32)
 
         def step():
-            ell.conv2d(g, sx.LAYOUT_PF, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
-        hX = torch.from_numpy(x_pf).pin_memory()
-        hY = torch.empty((Cc, H, W, Bl), dtype=torch.float32).pin_memory()
+            ell.conv2d(g, layout, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
+        hX = torch.from_numpy(x_in).pin_memory()
+        hY = torch.empty(oshape, dtype=torch.float32).pin_memory()
         h2d, d2h = hX.numel() * 4, hY.numel() * 4
 
         def e2e_step():
             dX.copy_(hX, non_blocking=True)
-            ell.conv2d(g, sx.LAYOUT_PF, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
+            ell.conv2d(g, layout, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
             hY.copy_(dY, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         working_set = (dX.numel() + dY.numel()) * 4
@@ -615,6 +651,13 @@ def measure(args, c):
         ag = {"ms_per_step": ag_sec * 1e3, "value": to_value(wk, job_bytes, ag_sec),
               "note": "SpMM + NCCL all-gather of Y into every rank's full buffer"}
 
+    fused = None
+    if fused_step is not None:
+        n_f = max(3, min(args.steps, 10))
+        f_sec = timed(fused_step, n_f, 2, False) / n_f
+        fused = {"ms_per_step": f_sec * 1e3, "value": to_value(wk, job_bytes, f_sec),
+                 "note": "SpMM whose epilogue stores Y into every rank's full buffer over NVLink (peer stores) + barrier"}
+
     if rank == 0:
         metric, unit = metric_of(wk, args)
         peak, peak_kind = measured_peak()
@@ -641,6 +684,8 @@ def measure(args, c):
             line["e2e"] = e2e
         if ag:
             line["with_allgather"] = ag
+        if fused:
+            line["with_fused_allgather"] = fused
         if not args.no_cpu and world == 1:
             try:
                 run, frac, ckind, sample = cpu_sample_runner(args, wk)

@@ -181,6 +181,27 @@ int spx_comm_destroy(spx_comm* c);
  * the exchange step of row-sharded SpMM, src/ellpack_matmul.cpp:26 being the row loop it splits.) */
 int spx_allgather_rows(spx_comm* c, float* Y, uint64_t rows_per_rank, uint64_t ld, void* stream);
 
+/* Stream-ordered barrier over the communicator (a one-float all-reduce): when it completes on this
+ * rank's stream, every rank has finished the work it enqueued before its own call. */
+int spx_comm_barrier(spx_comm* c, void* stream);
+
+/* ---- peer buffers and the fused SpMM + all-gather ----------------------------------------- */
+/* Share a device allocation made with spx_malloc with the other ranks of this node (one process
+ * per GPU): export an opaque handle, send it to the peers by any host channel, open it there.
+ * The opened pointer addresses the exporter's memory over NVLink. */
+#define SPX_IPC_HANDLE_BYTES 64
+int spx_ipc_export(void* dptr, char handle[SPX_IPC_HANDLE_BYTES]);
+int spx_ipc_open(const char handle[SPX_IPC_HANDLE_BYTES], void** dptr);
+int spx_ipc_close(void* dptr);
+/* Row-sharded SpMM whose epilogue IS the all-gather: e holds this rank's rows, which occupy rows
+ * [row_offset, row_offset + m) of the full Y; every finished output vector is stored into each of
+ * the nbuffers (<= 8) full-size buffers Ys[g] (this rank's own buffer and its peers' buffers
+ * opened with spx_ipc_open), leading dimension ldy, with ordinary stores over NVLink, so the
+ * exchange overlaps the multiply.  Follow it with spx_comm_barrier before any rank reads Y.
+ * Same arithmetic as spx_spmm (the split is the row loop of src/ellpack_matmul.cpp:26). */
+int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                   float* const* Ys, uint32_t nbuffers, uint64_t row_offset, uint64_t ldy, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -345,7 +345,7 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
-    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->stage_dev);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
     delete e;
     return SPX_OK;
 }
@@ -391,6 +391,43 @@ int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const f
     if (!Y) return fail(SPX_ERR_ARG, "Y is null");
     if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
     return launch_spmm(e, X, C, ldx, bias, act, Y, ldy, (cudaStream_t)stream);
+}
+
+int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                   float* const* Ys, uint32_t nbuffers, uint64_t row_offset, uint64_t ldy, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (!Ys) return fail(SPX_ERR_ARG, "destination list is null");
+    if (e->m == 0 || C == 0) return SPX_OK;
+    if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
+    if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    return launch_spmm_bcast(e, X, C, ldx, bias, act, Ys, nbuffers, row_offset, ldy, (cudaStream_t)stream);
+}
+
+int spx_ipc_export(void* dptr, char handle[SPX_IPC_HANDLE_BYTES])
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == SPX_IPC_HANDLE_BYTES, "IPC handle size");
+    if (!dptr || !handle) return fail(SPX_ERR_ARG, "null argument");
+    cudaIpcMemHandle_t h;
+    SPX_CUDA(cudaIpcGetMemHandle(&h, dptr));
+    memcpy(handle, &h, sizeof(h));
+    return SPX_OK;
+}
+
+int spx_ipc_open(const char handle[SPX_IPC_HANDLE_BYTES], void** dptr)
+{
+    if (!dptr || !handle) return fail(SPX_ERR_ARG, "null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    SPX_CUDA(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return SPX_OK;
+}
+
+int spx_ipc_close(void* dptr)
+{
+    if (dptr) SPX_CUDA(cudaIpcCloseMemHandle(dptr));
+    return SPX_OK;
 }
 
 int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void* stream)

@@ -17,6 +17,7 @@
 struct spx_comm {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1, device = 0;
+    float* token = nullptr;      // one float, operand of the barrier's all-reduce
 };
 
 namespace {
@@ -27,6 +28,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
 };
@@ -43,8 +45,9 @@ NcclApi& api()
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(a.lib, "ncclCommInitRank"));
         a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(a.lib, "ncclCommDestroy"));
         a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(a.lib, "ncclAllGather"));
+        a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(a.lib, "ncclAllReduce"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(a.lib, "ncclGetErrorString"));
-        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather && a.GetErrorString;
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather && a.AllReduce && a.GetErrorString;
     });
     return a;
 }
@@ -91,13 +94,29 @@ int spx_comm_create(int rank, int world, const char id[SPX_UNIQUE_ID_BYTES], spx
         delete c;
         return spx::fail(SPX_ERR_COMM, "ncclCommInitRank: %s", api().GetErrorString(r));
     }
+    cudaError_t err = cudaMalloc(&c->token, sizeof(float));
+    if (err == cudaSuccess) err = cudaMemset(c->token, 0, sizeof(float));
+    if (err != cudaSuccess) {
+        api().CommDestroy(c->comm);
+        delete c;
+        return spx::fail(SPX_ERR_CUDA, "communicator: token allocation failed: %s", cudaGetErrorString(err));
+    }
     *out = c;
+    return SPX_OK;
+}
+
+int spx_comm_barrier(spx_comm* c, void* stream)
+{
+    if (!c || !c->comm) return spx::fail(SPX_ERR_ARG, "communicator is null");
+    ncclResult_t r = api().AllReduce(c->token, c->token, 1, ncclFloat, ncclSum, c->comm, (cudaStream_t)stream);
+    if (r != ncclSuccess) return spx::fail(SPX_ERR_COMM, "ncclAllReduce: %s", api().GetErrorString(r));
     return SPX_OK;
 }
 
 int spx_comm_destroy(spx_comm* c)
 {
     if (!c) return SPX_OK;
+    cudaFree(c->token);
     if (c->comm && api().ok) api().CommDestroy(c->comm);
     delete c;
     return SPX_OK;

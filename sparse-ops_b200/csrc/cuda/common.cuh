@@ -33,6 +33,9 @@ struct spx_ell {
     // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
     void* stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
+    // Scratch of the NCHW convolution path: the input and output in [C,H,W,B] order (conv.cu).
+    void* conv_scratch = nullptr;
+    size_t conv_scratch_bytes = 0;
 };
 
 namespace spx {
@@ -80,6 +83,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 namespace spx {
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s);
+int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s);
 int launch_spmv(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                   const float* bias, int act, float* out, cudaStream_t s);

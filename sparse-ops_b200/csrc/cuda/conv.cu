@@ -94,6 +94,32 @@ conv_direct_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ ta
 }
 
 
+// dst[c * rows + r] = src[r * cols + c]: used to run NCHW tensors ([B][C*H*W]) through the
+// [C,H,W,B] kernel ([C*H*W][B]) and back.  32 x 32 tiles through padded shared memory, both
+// sides coalesced.
+template <bool ROWS_ON_X>   // which dimension is the long one and therefore rides on gridDim.x
+__global__ void __launch_bounds__(256)
+transpose2d_kernel(const float* __restrict__ src, uint64_t rows, uint64_t cols, float* __restrict__ dst)
+{
+    __shared__ float t[32][33];
+    const uint64_t c0 = (uint64_t)(ROWS_ON_X ? blockIdx.y : blockIdx.x) * 32;
+    const uint64_t r0 = (uint64_t)(ROWS_ON_X ? blockIdx.x : blockIdx.y) * 32;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        const uint64_t r = r0 + ty + i;
+        const uint64_t c = c0 + tx;
+        if (r < rows && c < cols) t[ty + i][tx] = src[(size_t)r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        const uint64_t c = c0 + ty + i;
+        const uint64_t r = r0 + tx;
+        if (r < rows && c < cols) dst[(size_t)c * rows + r] = t[tx][ty + i];
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // conv_pf_tile_kernel: the fast path for the [C,H,W,B] layout with B % 4 == 0.
 //
@@ -260,13 +286,37 @@ static int launch_tile_qb(const spx_ell* e, const TileParams& tp, dim3 grid, siz
     return SPX_OK;
 }
 
+// Shapes the tiled kernel covers: batch a multiple of 4, one channel of the tile's receptive field
+// within the shared-memory budget, grid within limits.
+static bool pf_tile_covers(const ConvParams& p)
+{
+    static const bool disabled = [] { const char* v = getenv("SPX_CONV_DIRECT"); return v && v[0] == '1'; }();
+    if (disabled || p.B % 4 != 0) return false;
+    const size_t THin = (kTileH - 1) * p.sH + (p.kH - 1) * p.dH + 1, TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
+    uint32_t BT = 0;
+    for (uint32_t c = 32; c >= 4; c -= 4) if (p.B % c == 0) { BT = c; break; }
+    if (!BT || THin * TWin * BT * sizeof(float) > 100 * 1024) return false;
+    const uint64_t tiles = (uint64_t)((p.Wo + kTileW - 1) / kTileW) * ((p.Ho + kTileH - 1) / kTileH);
+    return tiles <= 0x7fffffffull && (p.Cout + kTileWarps - 1) / kTileWarps <= 65535 && p.B / BT <= 65535;
+}
+
+static int transpose2d(const float* src, uint64_t rows, uint64_t cols, float* dst, cudaStream_t s)
+{
+    const uint64_t rt = (rows + 31) / 32, ct = (cols + 31) / 32;
+    const bool rows_on_x = rows >= cols;
+    const uint64_t gx = rows_on_x ? rt : ct, gy = rows_on_x ? ct : rt;
+    if (gx > 0x7fffffffull || gy > 65535) return fail(SPX_ERR_LIMIT, "conv2d: tensor too large to transpose");
+    if (rows_on_x) transpose2d_kernel<true><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(src, rows, cols, dst);
+    else           transpose2d_kernel<false><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(src, rows, cols, dst);
+    SPX_LAUNCH_CHECK("transpose2d_kernel");
+    return SPX_OK;
+}
+
 // Returns -1 when the shape is not covered (caller falls back to the direct kernel).
 static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const float* in, const float* bias, int act,
                                float* out, cudaStream_t s)
 {
-    static const bool disabled = [] { const char* v = getenv("SPX_CONV_DIRECT"); return v && v[0] == '1'; }();
-    if (disabled) return -1;
-    if (p.B % 4 != 0) return -1;
+    if (!pf_tile_covers(p)) return -1;
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
     // batch entries per CTA: the largest multiple of 4 that divides B and is <= 32
     uint32_t BT = 0;
@@ -327,6 +377,27 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     if (layout == SPX_LAYOUT_PF && e->r) {
         int rc2 = launch_conv_pf_tile(e, p, in, bias, act, out, s);
         if (rc2 != -1) return rc2;           // -1: shape not covered by the tiled kernel
+    }
+    if (layout == SPX_LAYOUT_NCHW && e->r && B > 1 && pf_tile_covers(p)) {
+        // NCHW: transpose to [C,H,W,B] in per-handle scratch, run the tiled kernel, transpose back.
+        // Two extra streaming passes over input and output (about 7 % of the kernel's time at
+        // 256 channels) instead of a second gather kernel; arithmetic per element is unchanged.
+        const size_t in_elems = (size_t)g->Cin * g->H * g->W * B, out_elems = (size_t)g->Cout * g->Ho * g->Wo * B;
+        const size_t need = (in_elems + out_elems) * sizeof(float) + 512;
+        if (e->conv_scratch_bytes < need) {
+            if (e->conv_scratch) cudaFree(e->conv_scratch);
+            e->conv_scratch = nullptr;
+            e->conv_scratch_bytes = 0;
+            SPX_CUDA(cudaMalloc(&e->conv_scratch, need));
+            e->conv_scratch_bytes = need;
+        }
+        float* in_pf = static_cast<float*>(e->conv_scratch);
+        float* out_pf = in_pf + ((in_elems + 63) / 64) * 64;
+        rc = transpose2d(in, B, (uint64_t)g->Cin * g->H * g->W, in_pf, s);
+        if (rc != SPX_OK) return rc;
+        rc = launch_conv_pf_tile(e, p, in_pf, bias, act, out_pf, s);
+        if (rc == SPX_OK) return transpose2d(out_pf, (uint64_t)g->Cout * g->Ho * g->Wo, B, out, s);
+        if (rc != -1) return rc;
     }
     const uint64_t per_m = (uint64_t)g->Ho * g->Wo * B;
     const uint64_t gx = (per_m + 255) / 256;

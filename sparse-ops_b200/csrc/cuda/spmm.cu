@@ -23,6 +23,17 @@
 namespace {
 
 constexpr int kGatherWarps = 8;
+constexpr int kMaxPeers = 8;
+
+// Destinations of the epilogue.  Plain SpMM: one pointer (this GPU's Y).  Row-sharded SpMM with
+// the all-gather fused in: the full Y buffer of every rank (this GPU's own and its peers' buffers
+// mapped over NVLink); each finished output vector is stored to all of them with ordinary 16-byte
+// stores, so the exchange overlaps the multiply instead of following it.
+struct PeerOut {
+    float* p[kMaxPeers];
+    int n;
+    uint64_t row0;      // first row of this rank's slab inside the full buffers
+};
 
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
@@ -42,7 +53,7 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
                 uint32_t m, uint32_t pitch,
                 const float* __restrict__ X, uint32_t C, uint64_t ldx,
-                const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
+                const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -100,7 +111,8 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
                 o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
             }
-            *reinterpret_cast<float4*>(Y + (size_t)row * ldy + c0 + 128 * v) = o;
+            const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 128 * v;
+            for (int g = 0; g < out.n; ++g) *reinterpret_cast<float4*>(out.p[g] + at) = o;
         }
     }
 }
@@ -112,7 +124,7 @@ spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ id
                    const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
                    uint32_t m, uint32_t pitch,
                    const float* __restrict__ X, uint32_t C, uint64_t ldx,
-                   const float* __restrict__ bias, int act, float* __restrict__ Y, uint64_t ldy)
+                   const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -163,7 +175,11 @@ spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ id
     }
 #pragma unroll
     for (int v = 0; v < NV; ++v)
-        if (on[v]) Y[(size_t)row * ldy + c0 + 32 * v] = spx::apply_act(acc[v], act);
+        if (on[v]) {
+            const float o = spx::apply_act(acc[v], act);
+            const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 32 * v;
+            for (int g = 0; g < out.n; ++g) out.p[g][at] = o;
+        }
 }
 
 }  // namespace
@@ -200,10 +216,26 @@ static uint32_t gather_wpb(const spx_ell* e, uint32_t panels)
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s)
 {
+    float* one[1] = { Y };
+    return launch_spmm_bcast(e, X, C, ldx, bias, act, one, 1, 0, ldy, s);
+}
+
+int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s)
+{
     if (e->m == 0 || C == 0) return SPX_OK;
+    if (npeers == 0 || npeers > (uint32_t)kMaxPeers) return fail(SPX_ERR_LIMIT, "spmm: 1..%d destination buffers supported", kMaxPeers);
+    PeerOut out{};
+    out.n = (int)npeers;
+    out.row0 = row0;
+    bool aligned = true;
+    for (uint32_t g = 0; g < npeers; ++g) {
+        if (!Ys[g]) return fail(SPX_ERR_ARG, "spmm: destination %u is null", g);
+        out.p[g] = Ys[g];
+        aligned = aligned && (reinterpret_cast<uintptr_t>(Ys[g]) & 15) == 0;
+    }
     const bool vec_ok = (C % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(X) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+                        ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && aligned;
     if (vec_ok) {
         const int nv = gather_nv(e->n, C);
         const uint32_t panels = (C + 128 * nv - 1) / (128 * nv);
@@ -211,10 +243,10 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
         dim3 grid((e->m + wpb - 1) / wpb, panels);
         if (nv == 2)
             spmm_gather_vec<2, 4><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                           X, C, ldx, bias, act, Y, ldy);
+                                                           X, C, ldx, bias, act, out, ldy);
         else
             spmm_gather_vec<1, 8><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                           X, C, ldx, bias, act, Y, ldy);
+                                                           X, C, ldx, bias, act, out, ldy);
         SPX_LAUNCH_CHECK("spmm_gather_vec");
     } else {
         const int nv = C > 32 ? 2 : 1;
@@ -223,10 +255,10 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
         dim3 grid((e->m + wpb - 1) / wpb, panels);
         if (nv == 2)
             spmm_gather_scalar<2><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                           X, C, ldx, bias, act, Y, ldy);
+                                                           X, C, ldx, bias, act, out, ldy);
         else
             spmm_gather_scalar<1><<<grid, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                           X, C, ldx, bias, act, Y, ldy);
+                                                           X, C, ldx, bias, act, out, ldy);
         SPX_LAUNCH_CHECK("spmm_gather_scalar");
     }
     return SPX_OK;

@@ -19,6 +19,7 @@ ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 LAYOUT_PF, LAYOUT_NCHW = 0, 1
 OP_RELU, OP_SIGMOID, OP_TANH, OP_ADD = 1, 2, 3, 4
 UNIQUE_ID_BYTES = 128
+IPC_HANDLE_BYTES = 64
 
 
 class SpxError(RuntimeError):
@@ -91,6 +92,12 @@ SIGNATURES = {
     "spx_comm_create": (C.c_int, [C.c_int, C.c_int, C.c_char_p, C.POINTER(_vp)]),
     "spx_comm_destroy": (C.c_int, [_vp]),
     "spx_allgather_rows": (C.c_int, [_vp, _vp, C.c_uint64, C.c_uint64, _vp]),
+    "spx_comm_barrier": (C.c_int, [_vp, _vp]),
+    "spx_ipc_export": (C.c_int, [_vp, C.c_char_p]),
+    "spx_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(_vp)]),
+    "spx_ipc_close": (C.c_int, [_vp]),
+    "spx_spmm_bcast": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint64, _vp, C.c_int, C.POINTER(_vp), C.c_uint32, C.c_uint64,
+                                 C.c_uint64, _vp]),
 }
 
 _STATUS_FREE = {"spx_last_error", "spx_version", "spx_launch_count"}

@@ -65,6 +65,41 @@ def main():
     want = orc.spmm(orc.encode(W), X, b, act=1)
     assert np.array_equal(dY.cpu().numpy()[:m].view(np.uint32), want.view(np.uint32)), "row-sharded SpMM differs"
 
+    # 1b. the same exchange fused into the SpMM epilogue: every rank stores its rows straight into
+    # all ranks' full buffers (peers' buffers opened over IPC), then a stream-ordered barrier
+    buf = C.c_void_p()
+    nbytes = per * world * Cc * 4
+    lib.spx_malloc(C.byref(buf), nbytes)
+    lib.spx_memset(buf, 0xff, nbytes, 0)
+    torch.cuda.synchronize()
+    handle = C.create_string_buffer(sx.IPC_HANDLE_BYTES)
+    lib.spx_ipc_export(buf, handle)
+    handles = [None] * world
+    dist.all_gather_object(handles, handle.raw)
+    ptrs, opened = [], []
+    for g in range(world):
+        if g == rank:
+            ptrs.append(buf.value)
+        else:
+            pp = C.c_void_p()
+            lib.spx_ipc_open(handles[g], C.byref(pp))
+            ptrs.append(pp.value)
+            opened.append(pp)
+    dist.barrier()                                   # every buffer is initialised before anyone writes
+    arr = (C.c_void_p * world)(*ptrs)
+    lib.spx_spmm_bcast(h.h, dX.data_ptr(), Cc, Cc, dB.data_ptr(), sx.ACT_RELU, arr, world, rank * per, Cc, stream)
+    lib.spx_comm_barrier(comm, stream)
+    torch.cuda.synchronize()
+    got = np.empty((per * world, Cc), np.float32)
+    lib.spx_memcpy_d2h(got.ctypes.data_as(C.c_void_p), buf, nbytes, 0)
+    lib.spx_device_sync()
+    assert np.array_equal(got[:m].view(np.uint32), want.view(np.uint32)), "fused SpMM + all-gather differs"
+    dist.barrier()
+    for pp in opened:
+        lib.spx_ipc_close(pp)
+    dist.barrier()
+    lib.spx_free(buf)
+
     # 2. + 3. model: 3 layers, relu/relu/none (bit-exact end to end), out features not divisible by world
     dims, B = [64, 96, 80, 30 + world - 1], 8 * world
     Ws = [sparse(rng, dims[i + 1], dims[i], 0.3, 0.3) for i in range(3)]
