@@ -84,6 +84,8 @@ int set_row_order(spx_ell* e, const uint32_t* host_nnz)
     for (size_t k = 1; k < start.size(); ++k) start[k] += start[k - 1];
     std::vector<uint32_t> order(e->m);
     for (uint32_t i = 0; i < e->m; ++i) order[start[e->r - host_nnz[i]]++] = i;
+    e->long_rows = 0;
+    for (uint32_t i = 0; i < e->m; ++i) e->long_rows += host_nnz[i] >= 512 ? 1u : 0u;
     if (!e->row_order) SPX_CUDA(cudaMalloc(&e->row_order, (size_t)e->m * sizeof(uint32_t)));
     SPX_CUDA(cudaMemcpy(e->row_order, order.data(), (size_t)e->m * sizeof(uint32_t), cudaMemcpyHostToDevice));
     return SPX_OK;

@@ -26,6 +26,7 @@ struct spx_ell {
     // warp one row take rows in this order, so the warps of a CTA get rows of equal length
     // (no warp idles behind a long row) and the longest rows start first.
     uint32_t* row_order = nullptr;   // m row ids
+    uint32_t long_rows = 0;          // rows with at least 512 stored entries (a prefix of row_order)
     // Lazily built, cached conv tap table: idx decoded to packed (cin, kh, kw) for one
     // kernel shape (conv.cu); keyed by (kH, kW).
     uint32_t* taps = nullptr;
