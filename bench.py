@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
     ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
+    ap.add_argument("--batch", type=int, default=0, help="cfg3_mlp: override the batch size")
     ap.add_argument("--nchw", action="store_true", help="cfg4_conv: NCHW tensors instead of [C,H,W,B]")
     ap.add_argument("--rows", type=int, default=0, help="cfg5_spmm: override the row count (profiling on a smaller case)")
     ap.add_argument("--cols", type=int, default=0, help="cfg5_spmm: override C, the dense column count")
@@ -203,7 +204,7 @@ def build_workload(args, rank: int, world: int):
         return dict(kind="spmv", m=m, n=d["n"], C=1, rows=hi - lo, row0=lo, csr=csr, x=d["x"], bias=d["bias"][lo:hi].copy(),
                     desc=f"SpMV {m}x{m} iid sparsity {args.sparsity}, bias")
     if w == "cfg3_mlp":
-        d = wl.cfg3(s)
+        d = wl.cfg3(s, batch=args.batch or None)
         return dict(kind="mlp", **d, desc=f"sparse MLP {'-'.join(map(str, d['dims']))}, 90% sparse, batch {d['B']}")
     if w == "cfg4_conv":
         d = wl.cfg4(s, layers=1)

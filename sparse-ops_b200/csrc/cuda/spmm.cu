@@ -145,6 +145,74 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// spmm_gather_sub<LPR>: narrow X (C <= 4*LPR, LPR = 8 or 16).  A full warp per row would leave
+// most lanes idle, so LPR lanes share a row and a warp carries 32/LPR rows of the sorted schedule
+// (neighbours there have near-equal lengths).  Same chain per output element as spmm_gather_vec.
+// ---------------------------------------------------------------------------------------
+template <int LPR, int BM>   // BM: entries loaded per lane and batch (LPR*BM gathers in flight per row)
+__global__ void __launch_bounds__(kGatherWarps * 32, 4)
+spmm_gather_sub(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+                const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                uint32_t m, uint32_t pitch,
+                const float* __restrict__ X, uint32_t C, uint64_t ldx,
+                const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy)
+{
+    constexpr int RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31;
+    const int sl = lane % LPR;
+    const uint32_t slot = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const bool live = slot < m;
+    const uint32_t row = live ? __ldg(row_order + slot) : 0u;
+    const uint32_t c0 = 4u * sl;
+    const bool on = live && c0 < C;
+
+    const float b = (live && bias) ? __ldg(bias + row) : 0.0f;
+    float4 acc = make_float4(b, b, b, b);
+    const uint32_t nn = live ? __ldg(nnz + row) : 0u;
+    const uint32_t nmax = __reduce_max_sync(0xffffffffu, nn);       // the warp runs to its longest row
+    const float* __restrict__ w = Wd + (size_t)row * pitch;
+    const uint32_t* __restrict__ k = idx + (size_t)row * pitch;
+
+    constexpr int NB = LPR * BM;
+    for (uint32_t j0 = 0; j0 < nmax; j0 += NB) {
+        float wl[BM];
+        uint32_t kl[BM];
+#pragma unroll
+        for (int h = 0; h < BM; ++h) {
+            wl[h] = 0.0f;
+            kl[h] = 0;
+            if (j0 + h * LPR + sl < nn) {
+                wl[h] = __ldg(w + j0 + h * LPR + sl);
+                kl[h] = __ldg(k + j0 + h * LPR + sl);
+            }
+        }
+        const uint32_t cnt = j0 < nn ? min((uint32_t)NB, nn - j0) : 0u;      // entries of this lane's row in the batch
+        float wt[NB];
+        float4 xv[NB];
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            wt[u] = __shfl_sync(0xffffffffu, wl[u / LPR], u % LPR, LPR);
+            const uint32_t kt = __shfl_sync(0xffffffffu, kl[u / LPR], u % LPR, LPR);
+            xv[u] = (on && (uint32_t)u < cnt) ? ldg4(X + (size_t)kt * ldx + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u)
+            if ((uint32_t)u < cnt) fma4(acc, wt[u], xv[u]);
+    }
+    if (on) {
+        float4 o = acc;
+        if (act != SPX_ACT_NONE) {
+            o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
+            o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
+        }
+        const size_t at = (size_t)(out.row0 + row) * ldy + c0;
+#pragma unroll
+        for (int g = 0; g < kMaxPeers; ++g)
+            if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+    }
+}
+
 // Scalar variant for C % 4 != 0 or unaligned operands: lane owns columns c0 + 32*v + lane.
 template <int NV>
 __global__ void __launch_bounds__(kGatherWarps * 32)
@@ -284,7 +352,21 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
     }
     const bool vec_ok = (C % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
                         ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && aligned;
-    if (vec_ok) {
+    if (vec_ok && C <= 64) {
+        const int lpr = C <= 32 ? 8 : 16;
+        const uint32_t rpw = 32 / lpr;
+        const uint32_t warps = (e->m + rpw - 1) / rpw;
+        uint32_t wpb = 8;
+        while (wpb > 1 && (uint64_t)((warps + wpb - 1) / wpb) < (uint64_t)sm_count(e->device) * 8) wpb >>= 1;
+        const uint32_t blocks = (warps + wpb - 1) / wpb;
+        if (lpr == 8)
+            spmm_gather_sub<8, 2><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                          X, C, ldx, bias, act, out, ldy);
+        else
+            spmm_gather_sub<16, 1><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                           X, C, ldx, bias, act, out, ldy);
+        SPX_LAUNCH_CHECK("spmm_gather_sub");
+    } else if (vec_ok) {
         const int nv = gather_nv(e->n, C);
         // A row is one dependent chain of gathers, G rows of X per round trip to L2 (about a
         // microsecond under load).  When the longest row's chain is a large part of the whole
