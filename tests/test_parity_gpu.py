@@ -335,3 +335,35 @@ def test_pools_bit_exact(lib, orc, golden, cuda, B, C, H, W, k, s, pad):
     if (B, C, H, W) == (3, 5, 9, 8):        # the reference binary's own outputs on this tensor
         assert_bit_equal(out.cpu().numpy().transpose(3, 0, 1, 2), golden["pool_max_ref"], "maxpool vs reference")
         assert_bit_equal(gap.cpu().numpy().T, golden["pool_gap_ref"], "gap vs reference")
+
+
+def test_config5_shard_skewed_rows_vs_oracle(lib, orc, cuda):
+    """The 8-GPU row shard of config 5 (32768 power-law rows, r = 2048, n = 65536) built from CSR,
+    against the oracle on a narrower X, plus: two half shards reproduce the whole bit for bit."""
+    import workloads as wl
+    rows, n, C = 32768, 65536, 64
+    rowptr, col, val = wl.cfg5_rows(0, rows, n=n)
+    h = lib.ell_create_csr(rows, n, rowptr, col, val)
+    assert h.r == 2048 and h.nnz_total == len(col)
+    X = wl.cfg5_dense_operand(n, C)
+    dX = dev(X, cuda)
+    dY = torch.full((rows, C), float("nan"), device=cuda, dtype=torch.float32)
+    h.spmm(dX.data_ptr(), C, C, 0, sx.ACT_NONE, dY.data_ptr(), C)
+    torch.cuda.synchronize()
+    Wd, idx, nnz = wl.csr_to_ell(rows, rowptr, col, val)
+    from oracle import EllArrays
+    want = orc.spmm(EllArrays(rows, n, Wd.shape[1], Wd, idx, nnz), X, None)
+    assert_bit_equal(dY.cpu().numpy(), want, "config 5 shard")
+    half = rows // 2
+    for g in range(2):
+        rp, cc, vv = wl.cfg5_rows(g * half, half, n=n)
+        hg = lib.ell_create_csr(half, n, rp, cc, vv)
+        out = torch.empty((half, C), device=cuda, dtype=torch.float32)
+        hg.spmm(dX.data_ptr(), C, C, 0, sx.ACT_NONE, out.data_ptr(), C)
+        torch.cuda.synchronize()
+        assert_bit_equal(out.cpu().numpy(), want[g * half:(g + 1) * half], f"half shard {g}")
+    # SpMV on the same skewed matrix (long and short rows share warps)
+    x = X[:, 0].copy()
+    y = gpu_spmv(h, x, None, cuda)
+    E = EllArrays(rows, n, Wd.shape[1], Wd, idx, nnz)
+    assert (np.abs(y - orc.spmv(E, x, None)) <= SPMV_TOL * orc.absbound(E, x, None)).all()
