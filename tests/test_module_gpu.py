@@ -222,3 +222,30 @@ def test_model_resnet_style_graph_vs_torch(backend, cuda):
     r3 = F.relu(F.conv2d(F.relu(F.conv2d(p1, t(w2), t(b2), padding=1)), t(w3), t(b3), padding=1) + p1)
     want = torch.sigmoid(F.linear(r3.mean((2, 3)), t(wf), t(bf))).numpy()
     assert np.abs(got - want).max() <= 1e-4
+
+
+def test_model_full_config3_vs_oracle(backend, orc, cuda):
+    """Config 3 at its full size (4096-4096-4096-4096-1000, 90 % sparse, batch 256) through
+    SparseOnnxModel.run against the oracle's layer loop: pre-sigmoid values are bit-identical
+    chains, the final sigmoid may differ by a few ulp."""
+    import onnx_wire
+    import workloads as wl
+    d = wl.cfg3(1.0)
+    m = _load(backend, onnx_wire.mlp_model(d["weights"], d["biases"], d["acts"], d["B"]))
+    assert [l["act"] for l in m.layer_summary()] == [1, 1, 1, 2]
+    x_mem = np.ascontiguousarray(d["x"].T)
+    y = m.run(x_mem.reshape(d["B"], -1)).ravel().reshape(-1, d["B"])
+    a = x_mem
+    for W, b in zip(d["weights"][:3], d["biases"][:3]):
+        a = orc.spmm(orc.encode(W), a, b, act=1)
+    want = orc.activation(orc.spmm(orc.encode(d["weights"][3]), a, d["biases"][3]), 2)
+    assert y.shape == want.shape == (1000, 256)
+    assert np.abs(y - want).max() <= 1e-6
+    # the hidden layers on their own, bit for bit, through the device-pointer call
+    E = backend.convert_to_ellpack(d["weights"][0])
+    dX = torch.from_numpy(x_mem).to(cuda)
+    dB = torch.from_numpy(d["biases"][0]).to(cuda)
+    dY = torch.empty((4096, 256), device=cuda)
+    backend.ellpack_matmul_device(E, dX.data_ptr(), 256, 256, dB.data_ptr(), 1, dY.data_ptr(), 256)
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), orc.spmm(orc.encode(d["weights"][0]), x_mem, d["biases"][0], act=1), "layer 1")

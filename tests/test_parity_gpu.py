@@ -367,3 +367,36 @@ def test_config5_shard_skewed_rows_vs_oracle(lib, orc, cuda):
     y = gpu_spmv(h, x, None, cuda)
     E = EllArrays(rows, n, Wd.shape[1], Wd, idx, nnz)
     assert (np.abs(y - orc.spmv(E, x, None)) <= SPMV_TOL * orc.absbound(E, x, None)).all()
+
+
+def test_config4_full_size_subset_vs_oracle(lib, orc, cuda):
+    """Config 4 at full size (256 -> 256 channels, 56 x 56, batch 32, 80 % sparse, bias + ReLU) on the
+    GPU in both layouts; the oracle checks 6 of the 256 output channels on 8 of the 32 images (the
+    scalar CPU restatement needs seconds for that slice, minutes for everything)."""
+    import workloads as wl
+    d = wl.cfg4(1.0)
+    Cc, H, W, B = d["C"], d["H"], d["W"], d["B"]
+    wt = d["weights"][0].reshape(Cc, -1)
+    E = orc.encode(wt)
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(Cc, Cc, 3, 3, H, W, pH=1, pW=1)
+    x = d["x_nchw"]
+    pf = np.ascontiguousarray(x.transpose(1, 2, 3, 0))
+    dB = dev(d["biases"][0], cuda)
+    dX = dev(pf, cuda)
+    out_pf = torch.full((Cc, H, W, B), float("nan"), device=cuda, dtype=torch.float32)
+    h.conv2d(g, sx.LAYOUT_PF, dX.data_ptr(), B, dB.data_ptr(), sx.ACT_RELU, out_pf.data_ptr())
+    dXn = dev(x, cuda)
+    out_n = torch.full((B, Cc, H, W), float("nan"), device=cuda, dtype=torch.float32)
+    h.conv2d(g, sx.LAYOUT_NCHW, dXn.data_ptr(), B, dB.data_ptr(), sx.ACT_RELU, out_n.data_ptr())
+    torch.cuda.synchronize()
+    got = out_pf.cpu().numpy()
+    assert np.isfinite(got).all()
+    # both layouts hold the same values
+    assert_bit_equal(out_n.cpu().numpy(), got.transpose(3, 0, 1, 2), "NCHW vs [C,H,W,B]")
+    rows = [0, 1, 77, 128, 200, 255]
+    from oracle import EllArrays
+    sub = EllArrays(len(rows), E.n, E.r, E.Wd[rows], E.idx[rows], E.nnz[rows])
+    gd = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+    want = orc.conv2d(sub, gd, 0, np.ascontiguousarray(pf[..., :8]), 8, d["biases"][0][rows], 1)
+    assert_bit_equal(got[rows][..., :8], want, "config 4 slice")
