@@ -182,7 +182,7 @@ def build_workload(args, rank: int, world: int):
         csr = wl.csr_from_blocks([(0, d["W"][lo:hi])], hi - lo)
         if w == "cfg1_spmm":
             return dict(kind="spmm", m=m, n=d["n"], C=d["C"], rows=hi - lo, row0=lo, csr=csr, X=d["X"],
-                        bias=d["bias"][lo:hi].copy(), dense_rows=d["W"][lo:hi],
+                        bias=d["bias"][lo:hi].copy(),
                         desc=f"SpMM {m}x{d['n']} iid p=0.1, C={d['C']}, bias")
         return dict(kind="spmv", m=m, n=d["n"], C=1, rows=hi - lo, row0=lo, csr=csr, x=d["x"],
                     bias=d["bias"][lo:hi].copy(), desc=f"SpMV {m}x{d['n']} iid p=0.1, bias")
@@ -523,11 +523,9 @@ def measure(args, c):
             dist.broadcast_object_list(idbuf, src=0)
             model.shard_rows(rank, world, idbuf[0])
             Bl, xl = B, x_mem
-            rows_pad = -(-model.out_features // world) * world
         else:
             Bl = B // world
             xl = np.ascontiguousarray(x_mem[:, rank * Bl:(rank + 1) * Bl])
-            rows_pad = model.out_features
         model.resize_buffers(Bl)
         # operands resident in the model's own device buffers; one step = one replay of the captured loop
         dX = torch.from_numpy(xl).to(dev)

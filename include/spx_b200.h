@@ -9,6 +9,9 @@
  *     current (spx_set_device) when the spx_ell handle was created.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Kernel
  *     entry points only enqueue work; they do not synchronise.
+ *   - A handle may be used from several host threads for kernel launches, but entry points
+ *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, the NCHW layout,
+ *     the *_host calls) must not run concurrently on the same handle.
  *   - There is no CPU fallback: without a usable CUDA device every compute entry point
  *     fails with SPX_ERR_CUDA.
  *
@@ -31,7 +34,6 @@ extern "C" {
 #define SPX_ERR_OOM       3   /* device or pinned-host allocation failed */
 #define SPX_ERR_LIMIT     4   /* size beyond what an entry point supports */
 #define SPX_ERR_COMM      5   /* NCCL / communicator failure */
-#define SPX_ERR_TIMEOUT   6   /* a bounded device-side wait gave up */
 
 /* Activation fused into a kernel epilogue.  RELU replaces the FUSE_RELU template flag of
  * ellpack_matmul_fused (src/ellpack_matmul.cpp:11,68-70); SIGMOID / TANH replace the

@@ -83,10 +83,12 @@ int spx_comm_create(int rank, int world, const char id[SPX_UNIQUE_ID_BYTES], spx
     if (world < 1 || rank < 0 || rank >= world) return spx::fail(SPX_ERR_ARG, "bad rank %d of %d", rank, world);
     int rc = need_api();
     if (rc != SPX_OK) return rc;
+    int device = 0;
+    SPX_CUDA(cudaGetDevice(&device));
     spx_comm* c = new spx_comm();
     c->rank = rank;
     c->world = world;
-    SPX_CUDA(cudaGetDevice(&c->device));
+    c->device = device;
     ncclUniqueId u;
     memcpy(&u, id, SPX_UNIQUE_ID_BYTES);
     ncclResult_t r = api().CommInitRank(&c->comm, world, u, rank);
