@@ -6,6 +6,7 @@
 
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -348,6 +349,7 @@ int spx_ell_destroy(spx_ell* e)
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
     cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
+    for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
     delete e;
     return SPX_OK;
 }
@@ -489,6 +491,42 @@ int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bi
     float* dX = reinterpret_cast<float*>(base);
     float* dB = reinterpret_cast<float*>(base + xb);
     float* dY = reinterpret_cast<float*>(base + xb + bb);
+    // Large, wide operands: the copies dominate (PCIe), so the call is pipelined over 256-column
+    // panels on three streams -- panel p+1 is copied in and panel p-1 copied out while panel p is
+    // multiplied (strided 2-D copies, 1 KiB per row).  Results are unchanged: a panel is exactly
+    // what one pass of the kernel computes anyway.
+    if (C >= 512 && C % 4 == 0 && (size_t)e->m * C * 4 >= ((size_t)64 << 20) && e->n) {
+        for (cudaStream_t& st : e->pipe_streams)
+            if (!st) SPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+        cudaStream_t s_in = e->pipe_streams[0], s_mm = e->pipe_streams[1], s_out = e->pipe_streams[2];
+        cudaEvent_t ev_in, ev_mm;
+        SPX_CUDA(cudaEventCreateWithFlags(&ev_in, cudaEventDisableTiming));
+        SPX_CUDA(cudaEventCreateWithFlags(&ev_mm, cudaEventDisableTiming));
+        cudaError_t err = cudaSuccess;
+        if (bias) err = cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, s_in);
+        for (uint32_t c0 = 0; c0 < C && err == cudaSuccess && rc == SPX_OK; c0 += 256) {
+            const uint32_t w = std::min<uint32_t>(256, C - c0);
+            err = cudaMemcpy2DAsync(dX + c0, (size_t)C * 4, X + c0, (size_t)C * 4, (size_t)w * 4, e->n, cudaMemcpyHostToDevice, s_in);
+            if (err == cudaSuccess) err = cudaEventRecord(ev_in, s_in);
+            if (err == cudaSuccess) err = cudaStreamWaitEvent(s_mm, ev_in, 0);
+            if (err != cudaSuccess) break;
+            rc = spx_spmm(e, dX + c0, w, C, bias ? dB : nullptr, act, dY + c0, C, s_mm);
+            if (rc != SPX_OK) break;
+            err = cudaEventRecord(ev_mm, s_mm);
+            if (err == cudaSuccess) err = cudaStreamWaitEvent(s_out, ev_mm, 0);
+            if (err == cudaSuccess)
+                err = cudaMemcpy2DAsync(Y + c0, (size_t)C * 4, dY + c0, (size_t)C * 4, (size_t)w * 4, e->m, cudaMemcpyDeviceToHost, s_out);
+        }
+        if (err == cudaSuccess) err = cudaStreamSynchronize(s_out);
+        // on an error the earlier streams may still be busy: drain them before the staging is reused
+        cudaStreamSynchronize(s_in);
+        cudaStreamSynchronize(s_mm);
+        cudaEventDestroy(ev_in);
+        cudaEventDestroy(ev_mm);
+        if (rc != SPX_OK) return rc;
+        if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "spmm_host: pipelined copy failed: %s", cudaGetErrorString(err));
+        return SPX_OK;
+    }
     if (e->n) SPX_CUDA(cudaMemcpyAsync(dX, X, (size_t)e->n * C * 4, cudaMemcpyHostToDevice, nullptr));
     if (bias) SPX_CUDA(cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, nullptr));
     rc = spx_spmm(e, dX, C, C, bias ? dB : nullptr, act, dY, C, nullptr);

@@ -37,6 +37,8 @@ struct spx_ell {
     // Scratch of the NCHW convolution path: the input and output in [C,H,W,B] order (conv.cu).
     void* conv_scratch = nullptr;
     size_t conv_scratch_bytes = 0;
+    // Streams of the pipelined host-buffer SpMM (copy in, multiply, copy out), created on first use.
+    cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
 };
 
 namespace spx {

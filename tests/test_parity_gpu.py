@@ -400,3 +400,23 @@ def test_config4_full_size_subset_vs_oracle(lib, orc, cuda):
     gd = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
     want = orc.conv2d(sub, gd, 0, np.ascontiguousarray(pf[..., :8]), 8, d["biases"][0][rows], 1)
     assert_bit_equal(got[rows][..., :8], want, "config 4 slice")
+
+
+def test_host_buffer_spmm_pipelined_panels(lib, orc, cuda):
+    """Wide, large operands take the panel-pipelined route of spx_spmm_host (three streams, strided
+    copies); the result must equal the plain route bit for bit, including a ragged last panel."""
+    rng = np.random.default_rng(31)
+    m, n, C = 30000, 900, 772            # m*C*4 = 92 MB >= 64 MB, C = 3 panels + 4 columns
+    W = sparse(rng, m, n, 0.02)
+    X = rng.uniform(-1, 1, (n, C)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    got = h.spmm_host(X, b, sx.ACT_RELU)
+    assert_bit_equal(got, gpu_spmm(h, X, b, sx.ACT_RELU, cuda), "pipelined host route vs device route")
+    assert_bit_equal(got[:500], orc.spmm(oracle_rows(E, 500), X, b[:500], act=1), "first rows vs oracle")
+
+
+def oracle_rows(E, k):
+    from oracle import EllArrays
+    return EllArrays(k, E.n, E.r, E.Wd[:k], E.idx[:k], E.nnz[:k])
