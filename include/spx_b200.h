@@ -132,6 +132,11 @@ int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const f
 /* y[i] = bias[i] + sum_j Wd[i,j] * x[idx[i,j]].  Replaces ellpack_matvec
  * (src/ellpack_matvec.cpp:20-147).  bias may be NULL. */
 int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void* stream);
+/* spx_spmv in the reference's own summation order (sixteen partial sums by j mod 16, then the
+ * pairwise tree of src/ellpack_matvec.cpp:88-96): bit-identical to the reference's AVX-512 path,
+ * slower than spx_spmv.  For checking.  Setting SPX_SPMV_REFERENCE_ORDER=1 in the environment
+ * routes spx_spmv here as well. */
+int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias, float* y, void* stream);
 /* Sparse convolution by implicit im2col; e is the ELLPACK of the weight flattened to
  * [Cout x Cin*kH*kW].  Replaces conv2d_patchmajor_tiled / conv2d_tiled_im2col_cmajor /
  * conv2d_tiled_im2col_fmajor / conv2d_rbm_fmajor_implicit (src/layers/conv_kernels.cpp:66-470). */

@@ -443,6 +443,15 @@ int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void
     return launch_spmv(e, x, bias, y, (cudaStream_t)stream);
 }
 
+int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias, float* y, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (e->m == 0) return SPX_OK;
+    if (!y) return fail(SPX_ERR_ARG, "y is null");
+    if (!x && e->nnz_total) return fail(SPX_ERR_ARG, "x is null");
+    return launch_spmv_reforder(e, x, bias, y, (cudaStream_t)stream);
+}
+
 int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                const float* bias, int act, float* out, void* stream)
 {

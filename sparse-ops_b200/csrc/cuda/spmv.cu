@@ -13,6 +13,8 @@
 // (a multiple of the SM count) so x is staged once per CTA.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace {
 
 template <int LPR>
@@ -89,6 +91,31 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     }
 }
 
+// Reference-order variant: reproduces the summation order of the reference's AVX-512 path bit for
+// bit (src/ellpack_matvec.cpp:72-99): sixteen partial sums, partial l takes entries j = l, l+16, ...
+// with one FMA each starting from 0; then lanes l and l+8, l and l+4, the two horizontal adds, and
+// finally bias + sum.  Sixteen lanes per row; slower than spmv_ell_kernel (4-byte loads, chains of
+// nnz/16), meant for checking, not for throughput.
+__global__ void __launch_bounds__(256)
+spmv_reforder_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+                     const uint32_t* __restrict__ nnz, uint32_t m, uint32_t pitch,
+                     const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y)
+{
+    const uint32_t l = threadIdx.x & 15;
+    const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const bool live = row < m;
+    const uint32_t nn = live ? __ldg(nnz + row) : 0u;
+    const float* __restrict__ w = Wd + (size_t)(live ? row : 0) * pitch;
+    const uint32_t* __restrict__ k = idx + (size_t)(live ? row : 0) * pitch;
+    float a = 0.0f;
+    for (uint32_t j = l; j < nn; j += 16) a = fmaf(__ldg(w + j), __ldg(x + __ldg(k + j)), a);
+    a = a + __shfl_xor_sync(0xffffffffu, a, 8);      // l with l+8
+    a = a + __shfl_xor_sync(0xffffffffu, a, 4);      // l with l+4
+    a = a + __shfl_xor_sync(0xffffffffu, a, 1);      // (0+1), (2+3)
+    a = a + __shfl_xor_sync(0xffffffffu, a, 2);      // their sum
+    if (live && l == 0) y[row] = (bias ? __ldg(bias + row) : 0.0f) + a;
+}
+
 template <int LPR, bool SMEM>
 int launch_one(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s,
                int threads, int blocks, size_t smem)
@@ -140,9 +167,20 @@ int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cu
 
 namespace spx {
 
+int launch_spmv_reforder(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s)
+{
+    if (e->m == 0) return SPX_OK;
+    const uint64_t threads = (uint64_t)e->m * 16;
+    spmv_reforder_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(e->Wd, e->idx, e->nnz, e->m, e->pitch, x, bias, y);
+    SPX_LAUNCH_CHECK("spmv_reforder_kernel");
+    return SPX_OK;
+}
+
 int launch_spmv(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s)
 {
     if (e->m == 0) return SPX_OK;
+    static const bool exact = [] { const char* v = getenv("SPX_SPMV_REFERENCE_ORDER"); return v && v[0] == '1'; }();
+    if (exact) return launch_spmv_reforder(e, x, bias, y, s);
     // Lanes per row from the mean row length: a lane consumes 4 entries per vector load.
     const double mean = e->m ? (double)e->nnz_total / e->m : 0.0;
     if (mean > 192.0) return launch_lpr<32>(e, x, bias, y, s);

@@ -81,6 +81,7 @@ SIGNATURES = {
     "spx_ell_decode_device": (C.c_int, [_vp, _vp, _vp]),
     "spx_spmm": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint64, _vp, C.c_int, _vp, C.c_uint64, _vp]),
     "spx_spmv": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "spx_spmv_reference_order": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "spx_conv2d": (C.c_int, [_vp, C.POINTER(ConvGeom), C.c_int, _vp, C.c_uint32, _vp, C.c_int, _vp, _vp]),
     "spx_conv2d_static": (C.c_int, [_vp, C.POINTER(ConvGeom), C.c_int, _vp, C.c_uint32, _vp, C.c_int, _vp, _vp]),
     "spx_eltwise": (C.c_int, [C.c_int, _vp, _vp, _vp, C.c_uint64, _vp]),

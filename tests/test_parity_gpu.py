@@ -420,3 +420,28 @@ def test_host_buffer_spmm_pipelined_panels(lib, orc, cuda):
 def oracle_rows(E, k):
     from oracle import EllArrays
     return EllArrays(k, E.n, E.r, E.Wd[:k], E.idx[:k], E.nnz[:k])
+
+
+@pytest.mark.parametrize("name", ["mm_a", "mm_b", "mm_c", "mm_d"])
+def test_spmv_reference_order_is_bit_exact(lib, orc, golden, cuda, name):
+    """The checking variant of SpMV reproduces the reference binary's result bit for bit."""
+    E = orc.encode(golden[name + "_W"])
+    h = gpu_ell(lib, E)
+    for bias, want in ((golden[name + "_bias"], golden[name + "_y_ref"]), (None, golden[name + "_ynobias_ref"])):
+        dx = dev(golden[name + "_x"], cuda)
+        dB = None if bias is None else dev(bias, cuda)
+        dy = torch.full((h.m,), float("nan"), device=cuda, dtype=torch.float32)
+        lib.spx_spmv_reference_order(h.h, ptr(dx), ptr(dB), ptr(dy), 0)
+        torch.cuda.synchronize()
+        assert_bit_equal(dy.cpu().numpy(), want, "reference-order spmv")
+    rng = np.random.default_rng(77)
+    W = sparse(rng, 1500, 2100, 0.07)
+    x = rng.uniform(-1, 1, 2100).astype(np.float32)
+    b = rng.standard_normal(1500).astype(np.float32)
+    E2 = orc.encode(W)
+    h2 = gpu_ell(lib, E2)
+    dy = torch.empty(1500, device=cuda)
+    dx2, db2 = dev(x, cuda), dev(b, cuda)
+    lib.spx_spmv_reference_order(h2.h, dx2.data_ptr(), db2.data_ptr(), dy.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert_bit_equal(dy.cpu().numpy(), orc.spmv(E2, x, b), "reference-order spmv vs oracle")
