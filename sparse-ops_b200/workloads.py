@@ -54,6 +54,37 @@ def csr_from_blocks(blocks, m: int):
     return rowptr, col, val
 
 
+def bernoulli_csr(seed: int, m: int, n: int, p: float, sigma=1.0, block_rows: int = 1024):
+    """CSR of an m x n matrix whose entries are kept iid with probability p, values N(0, sigma^2).
+    The keep mask is drawn block by block (the dense matrix never exists), each block from its own
+    stream so the blocks can be drawn by a few host threads; values only for the kept entries."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    def block(b):
+        r0 = b * block_rows
+        rows = min(block_rows, m - r0)
+        g = np.random.default_rng([seed, 7, b])
+        keep = np.flatnonzero(g.random(rows * n, dtype=np.float32) < np.float32(p))
+        rr = keep // n
+        v = g.standard_normal(len(keep), dtype=np.float32)
+        if sigma != 1.0:
+            v *= np.float32(sigma)
+        return (keep - rr * n).astype(np.uint32), np.bincount(rr, minlength=rows).astype(np.uint64), v
+
+    nblocks = (m + block_rows - 1) // block_rows
+    workers = max(1, min(16, os.cpu_count() or 1, nblocks))
+    with ThreadPoolExecutor(workers) as ex:
+        parts = list(ex.map(block, range(nblocks)))
+    rowptr = np.zeros(m + 1, dtype=np.uint64)
+    for b, (_, cnt, _) in enumerate(parts):
+        rowptr[b * block_rows + 1:b * block_rows + 1 + len(cnt)] = cnt
+    np.cumsum(rowptr, out=rowptr)
+    col = np.concatenate([p_[0] for p_ in parts]) if parts else np.zeros(0, np.uint32)
+    val = np.concatenate([p_[2] for p_ in parts]) if parts else np.zeros(0, np.float32)
+    return rowptr, col, val
+
+
 def csr_to_ell(m: int, rowptr, col, val):
     """Padded (Wd, idx, nnz) in the reference's host layout from CSR."""
     nnz = np.diff(rowptr).astype(np.uint32)
@@ -90,7 +121,7 @@ def cfg2_case(size: int, sparsity: float, seed: int = 43):
     sigma = 1.0 / np.sqrt(max(1.0, p * size))
     case_seed = seed + CFG2_SIZES.index(size) * len(CFG2_SPARSITIES) + CFG2_SPARSITIES.index(sparsity) \
         if size in CFG2_SIZES and sparsity in CFG2_SPARSITIES else seed
-    rowptr, col, val = csr_from_blocks(bernoulli_matrix(case_seed, size, size, p, sigma), size)
+    rowptr, col, val = bernoulli_csr(case_seed, size, size, p, sigma)
     x = _rng(case_seed, 1).uniform(-1, 1, size).astype(np.float32)
     bias = _rng(case_seed, 2).standard_normal(size).astype(np.float32)
     return dict(m=size, n=size, rowptr=rowptr, col=col, val=val, x=x, bias=bias)
