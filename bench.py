@@ -679,6 +679,13 @@ def measure(args, c):
                          "algorithmic_bytes_per_launch": per_gpu_bytes / max(1, launches_per_step) if kind != "mlp" else None,
                          "traffic": recorded_traffic(kernel_name, args.workload)},
         }
+        # SpMM and conv move one 4-byte operand per FMA through the L2 -> SM gather path / shared
+        # memory; that path, not HBM, is what their time tracks, so it is reported too.
+        if kind in ("spmm", "conv", "mlp"):
+            op_bytes = job_flops / 2.0 * 4.0 / world
+            line["roofline"]["operand_path"] = {
+                "what": "gathered X operands, 4 bytes per FMA (L2->SM for SpMM/MLP, shared memory for conv)",
+                "bytes_per_step": op_bytes, "achieved_tbps": op_bytes / sec / 1e12}
         if e2e:
             line["e2e"] = e2e
         if ag:
