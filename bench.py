@@ -680,7 +680,7 @@ def measure(args, c):
                          "traffic": recorded_traffic(kernel_name, args.workload)},
         }
         # SpMM and conv move one 4-byte operand per FMA through the L2 -> SM gather path / shared
-        # memory; that path, not HBM, is what their time tracks (see DESIGN.md), so it is reported too.
+        # memory; that path, not HBM, is what their time tracks, so it is reported too.
         if kind in ("spmm", "conv", "mlp"):
             op_bytes = job_flops / 2.0 * 4.0 / world
             line["roofline"]["operand_path"] = {
