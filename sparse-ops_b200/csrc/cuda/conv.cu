@@ -123,8 +123,8 @@ transpose2d_kernel(const float* __restrict__ src, uint64_t rows, uint64_t cols, 
 // ---------------------------------------------------------------------------------------------
 // conv_pf_tile_kernel: the fast path for the [C,H,W,B] layout with B % 4 == 0.
 //
-// A CTA owns a tile of 4 x 8 output positions x BT batch entries x 16 output channels (one warp
-// per output channel, accumulators in registers for the whole kernel).  It walks the input
+// A CTA owns a tile of 4 x 8 (2 x 8 at a full batch tile) output positions x BT batch entries x 16
+// (32) output channels (one warp per output channel, accumulators in registers for the whole kernel).  It walks the input
 // channels in chunks: the chunk's input patch (CC channels x the tile's receptive field x BT) is
 // staged in shared memory with 16-byte cp.async copies, positions outside the image are stored as
 // zeros (so a tap there contributes the operand 0.0f exactly like the reference's zero-filled
@@ -153,8 +153,10 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
-template <int QB, int MINB>   // QB: float4 groups per lane = BT / 4; MINB: CTAs per SM aimed for
-__global__ void __launch_bounds__(kTileWarps * 32, MINB)
+// QB: batch quads per output position (= BT / 4); G: float4 groups per lane, so a warp covers
+// 32*G/QB positions (kTileW wide); WARPS: output channels per CTA; MINB: CTAs per SM aimed for.
+template <int QB, int G, int WARPS, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ taps,
                     const uint32_t* __restrict__ nnz, uint32_t pitch, TileParams tp,
                     const float* __restrict__ in, const float* __restrict__ bias, int act,
@@ -165,27 +167,28 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
     const uint32_t BT = QB * 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t ty = blockIdx.x / tp.tilesX, tx = blockIdx.x % tp.tilesX;
-    const uint32_t oh0 = ty * kTileH, ow0 = tx * kTileW;
+    constexpr uint32_t TH = 32u * G / QB / kTileW;       // tile height in output positions
+    const uint32_t oh0 = ty * TH, ow0 = tx * kTileW;
     const uint32_t b0 = blockIdx.z * BT;
-    const uint32_t mo = blockIdx.y * kTileWarps + warp;
+    const uint32_t mo = blockIdx.y * WARPS + warp;
     const bool active = mo < p.Cout;
     const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;      // image row of staged row 0
     const int iw0 = (int)(ow0 * p.sW) - (int)p.pW;
     const uint32_t rowUnits = tp.TWin * QB;             // float4 units per staged row
 
-    // this lane's QB output positions: unit q = lane + 32 g -> (pixel, batch quad)
-    uint32_t off[QB];
+    // this lane's G output units: unit q = lane + 32 g -> (position, batch quad)
+    uint32_t off[G];
 #pragma unroll
-    for (int g = 0; g < QB; ++g) {
+    for (int g = 0; g < G; ++g) {
         const uint32_t q = lane + 32u * g;
         const uint32_t pix = q / QB, quad = q % QB;
         const uint32_t py = pix / kTileW, px = pix % kTileW;
         off[g] = ((py * p.sH) * tp.TWin + px * p.sW) * BT + quad * 4;
     }
     const float bv = (active && bias) ? __ldg(bias + mo) : 0.0f;
-    float4 acc[QB];
+    float4 acc[G];
 #pragma unroll
-    for (int g = 0; g < QB; ++g) acc[g] = make_float4(bv, bv, bv, bv);
+    for (int g = 0; g < G; ++g) acc[g] = make_float4(bv, bv, bv, bv);
 
     const uint32_t nn = active ? __ldg(nnz + mo) : 0u;
     const float* __restrict__ wrow = Wd + (size_t)(active ? mo : 0) * pitch;
@@ -196,7 +199,7 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
         const uint32_t c1 = min(p.Cin, c0 + tp.CC);
         // ---- stage the chunk: one warp per (channel, row) of the patch ----
         const uint32_t rows = (c1 - c0) * tp.THin;
-        for (uint32_t r = warp; r < rows; r += kTileWarps) {
+        for (uint32_t r = warp; r < rows; r += WARPS) {
             const uint32_t c = r / tp.THin, y = r % tp.THin;
             const int ih = ih0 + (int)y;
             const bool rowok = (unsigned)ih < p.H;
@@ -227,7 +230,7 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
                     const float wt = __shfl_sync(0xffffffffu, wl, t);
                     const float* xs = tile + __shfl_sync(0xffffffffu, tl, t);
 #pragma unroll
-                    for (int g = 0; g < QB; ++g) {
+                    for (int g = 0; g < G; ++g) {
                         const float4 xv = *reinterpret_cast<const float4*>(xs + off[g]);
                         acc[g].x = fmaf(wt, xv.x, acc[g].x);
                         acc[g].y = fmaf(wt, xv.y, acc[g].y);
@@ -243,7 +246,7 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
     }
     if (!active) return;
 #pragma unroll
-    for (int g = 0; g < QB; ++g) {
+    for (int g = 0; g < G; ++g) {
         const uint32_t q = lane + 32u * g;
         const uint32_t pix = q / QB, quad = q % QB;
         const uint32_t oh = oh0 + pix / kTileW, ow = ow0 + pix % kTileW;
@@ -274,14 +277,14 @@ static int ensure_taps(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
     return SPX_OK;
 }
 
-template <int QB, int MINB>
+template <int QB, int G, int WARPS, int MINB>
 static int launch_tile_qb(const spx_ell* e, const TileParams& tp, dim3 grid, size_t smem, const float* in,
                           const float* bias, int act, float* out, cudaStream_t s)
 {
-    auto kfn = conv_pf_tile_kernel<QB, MINB>;
+    auto kfn = conv_pf_tile_kernel<QB, G, WARPS, MINB>;
     cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
-    kfn<<<grid, kTileWarps * 32, smem, s>>>(e->Wd, e->taps, e->nnz, e->pitch, tp, in, bias, act, out);
+    kfn<<<grid, WARPS * 32, smem, s>>>(e->Wd, e->taps, e->nnz, e->pitch, tp, in, bias, act, out);
     SPX_LAUNCH_CHECK("conv_pf_tile_kernel");
     return SPX_OK;
 }
@@ -322,45 +325,45 @@ static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const floa
     uint32_t BT = 0;
     for (uint32_t c = 32; c >= 4; c -= 4) if (p.B % c == 0) { BT = c; break; }
     if (!BT) return -1;
+    static const int ctas = [] { const char* v = getenv("SPX_CONV_CTAS"); return v ? atoi(v) : 0; }();
+    static const int small_tile = [] { const char* v = getenv("SPX_CONV_SMALL_TILE"); return v ? atoi(v) : -1; }();
+    // Full batch tile (32 entries): 2 x 8 positions per warp and 32 warps (= output channels) per
+    // CTA instead of 4 x 8 positions and 16 warps: 64 registers per thread, twice the warps to hide
+    // the shared-memory latency, half the staging traffic per output channel.  Measured on
+    // 256 -> 256 channels, 56 x 56, batch 32: 1.89 ms against 2.03 ms.  SPX_CONV_SMALL_TILE=0 selects
+    // the larger tile.
+    const bool small = BT == 32 && small_tile != 0;
+    const uint32_t TH = small ? 2 : kTileH;
+    const uint32_t warps = small ? 32 : kTileWarps;
     TileParams tp{};
     tp.c = p;
     tp.BT = BT;
-    tp.THin = (kTileH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
+    tp.THin = (TH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
     tp.TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
     const size_t chanBytes = (size_t)tp.THin * tp.TWin * BT * sizeof(float);
-    static const int ctas = [] { const char* v = getenv("SPX_CONV_CTAS"); return v ? atoi(v) : 0; }();
     // Two CTAs per SM overlap one CTA's staging with the other's FMAs; with 8 float4 groups per
     // lane (batch 32) the accumulators need more than the 64 registers that allows.
-    const int per_sm = ctas == 1 || ctas == 2 ? ctas : (BT / 4 > 4 ? 1 : 2);
+    const int per_sm = small ? 1 : (ctas == 1 || ctas == 2 ? ctas : (BT / 4 > 4 ? 1 : 2));
     const size_t budget = per_sm == 2 ? 100 * 1024 : 200 * 1024;
     if (chanBytes > budget) return -1;
     tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
     // the per-nonzero shared-memory offset must fit 32 bits (it does: <= budget / 4)
     tp.tilesX = (p.Wo + kTileW - 1) / kTileW;
-    const uint32_t tilesY = (p.Ho + kTileH - 1) / kTileH;
+    const uint32_t tilesY = (p.Ho + TH - 1) / TH;
     const uint64_t tiles = (uint64_t)tp.tilesX * tilesY;
-    const uint32_t gy = (p.Cout + kTileWarps - 1) / kTileWarps, gz = p.B / BT;
+    const uint32_t gy = (p.Cout + warps - 1) / warps, gz = p.B / BT;
     if (tiles > 0x7fffffffull || gy > 65535 || gz > 65535) return -1;
     dim3 grid((unsigned)tiles, gy, gz);
     const size_t smem = chanBytes * tp.CC;
+    if (small) return launch_tile_qb<8, 4, 32, 1>(e, tp, grid, smem, in, bias, act, out, s);
+#define SPX_TILE_CASE(Q)                                                                                           \
+    case Q: return per_sm == 2 ? launch_tile_qb<Q, Q, kTileWarps, 2>(e, tp, grid, smem, in, bias, act, out, s)     \
+                               : launch_tile_qb<Q, Q, kTileWarps, 1>(e, tp, grid, smem, in, bias, act, out, s);
     switch (BT / 4) {
-    case 1: return per_sm == 2 ? launch_tile_qb<1, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<1, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 2: return per_sm == 2 ? launch_tile_qb<2, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<2, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 3: return per_sm == 2 ? launch_tile_qb<3, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<3, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 4: return per_sm == 2 ? launch_tile_qb<4, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<4, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 5: return per_sm == 2 ? launch_tile_qb<5, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<5, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 6: return per_sm == 2 ? launch_tile_qb<6, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<6, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 7: return per_sm == 2 ? launch_tile_qb<7, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<7, 1>(e, tp, grid, smem, in, bias, act, out, s);
-    case 8: return per_sm == 2 ? launch_tile_qb<8, 2>(e, tp, grid, smem, in, bias, act, out, s)
-                           : launch_tile_qb<8, 1>(e, tp, grid, smem, in, bias, act, out, s);
+        SPX_TILE_CASE(1) SPX_TILE_CASE(2) SPX_TILE_CASE(3) SPX_TILE_CASE(4)
+        SPX_TILE_CASE(5) SPX_TILE_CASE(6) SPX_TILE_CASE(7) SPX_TILE_CASE(8)
     }
+#undef SPX_TILE_CASE
     return -1;
 }
 
