@@ -30,8 +30,19 @@ struct SparseOnnxModel::Exec {
     std::unordered_map<std::string, float*> buf;      // tensor name -> device buffer
     std::unordered_map<std::string, uint64_t> rows;   // tensor name -> rows (elements per column)
     std::vector<void*> owned;
+    // Row-sharded mode with the exchange fused into the SpMM epilogue: for every MatMul output the
+    // full buffer of each rank (own pointer + peers' buffers opened over IPC), indexed by rank.
+    bool fused = false;
+    std::unordered_map<std::string, std::vector<float*>> peers;
+    std::vector<void*> opened;
+    spx_comm* comm = nullptr;          // not owned
     ~Exec() {
         if (graph) spx_graph_destroy(graph);
+        for (void* p : opened) spx_ipc_close(p);
+        if (fused && comm && stream) {
+            // every rank has unmapped the others' buffers before anybody frees its own
+            if (spx_comm_barrier(comm, stream) == SPX_OK) spx_stream_sync(stream);
+        }
         for (void* p : owned) spx_free(p);
         spx_free(d_bias);
         if (stream) spx_stream_destroy(stream);
@@ -315,6 +326,52 @@ void SparseOnnxModel::shard_rows(int rank, int world, const char* unique_id)
 
 void SparseOnnxModel::resize_buffers(uint32_t B) { build_exec(B); }
 
+// Every rank exports its full-size output buffers, the 64-byte handles travel through one
+// all-gather, and each rank maps its peers' buffers.  Any failure leaves the NCCL route in place.
+bool SparseOnnxModel::exchange_peer_buffers(Exec& ex, const std::vector<std::string>& names) const
+{
+    // Every rank runs the same two collectives whatever happens locally, so that a local failure
+    // can never leave the ranks in different modes: the handles travel in the first all-gather, a
+    // success flag per rank in the second; the fused route is taken only if every rank succeeded.
+    const size_t L = names.size(), hfloats = SPX_IPC_HANDLE_BYTES / sizeof(float), per = L * hfloats + 1;
+    std::vector<float> mine(per, 0.0f);
+    bool ok = true;
+    for (size_t i = 0; i < L && ok; ++i)
+        ok = spx_ipc_export(ex.buf.at(names[i]), reinterpret_cast<char*>(mine.data() + i * hfloats)) == SPX_OK;
+    float* d_all = nullptr;
+    check(spx_malloc(reinterpret_cast<void**>(&d_all), size_t(world_) * per * sizeof(float)), "handle exchange buffer");
+    std::vector<float> all(size_t(world_) * per, 0.0f);
+    auto gather = [&]() {
+        mine[per - 1] = ok ? 1.0f : 0.0f;
+        check(spx_memcpy_h2d(d_all + size_t(rank_) * per, mine.data(), per * sizeof(float), ex.stream), "handle exchange");
+        check(spx_allgather_rows(comm_, d_all, 1, per, ex.stream), "handle exchange");
+        check(spx_memcpy_d2h(all.data(), d_all, all.size() * sizeof(float), ex.stream), "handle exchange");
+        check(spx_stream_sync(ex.stream), "handle exchange");
+        for (int g = 0; g < world_; ++g) ok = ok && all[size_t(g) * per + per - 1] == 1.0f;
+    };
+    gather();                                       // handles + "export worked" flags
+    if (ok) {
+        for (size_t i = 0; i < L && ok; ++i) {
+            std::vector<float*> ptrs(world_, nullptr);
+            for (int g = 0; g < world_ && ok; ++g) {
+                if (g == rank_) { ptrs[g] = ex.buf.at(names[i]); continue; }
+                void* p = nullptr;
+                ok = spx_ipc_open(reinterpret_cast<const char*>(all.data() + size_t(g) * per + i * hfloats), &p) == SPX_OK;
+                if (ok) { ex.opened.push_back(p); ptrs[g] = static_cast<float*>(p); }
+            }
+            if (ok) ex.peers[names[i]] = std::move(ptrs);
+        }
+    }
+    gather();                                       // "mapping worked" flags
+    spx_free(d_all);
+    if (!ok) {
+        for (void* p : ex.opened) spx_ipc_close(p);
+        ex.opened.clear();
+        ex.peers.clear();
+    }
+    return ok;
+}
+
 void SparseOnnxModel::build_exec(uint32_t B) const
 {
     exec_.reset();
@@ -360,6 +417,16 @@ void SparseOnnxModel::build_exec(uint32_t B) const
         }
         alloc(L.outputs[0], rows, padded);
     }
+    if (world_ > 1 && comm_) {
+        ex->comm = comm_;
+        const char* off = std::getenv("SPX_TP_FUSED");
+        if (!(off && off[0] == '0')) {
+            std::vector<std::string> names;
+            for (const auto& L : layers_)
+                if (L.op == LayerOp::MatMul && L.shard) names.push_back(L.outputs[0]);
+            if (!names.empty()) ex->fused = exchange_peer_buffers(*ex, names);
+        }
+    }
     exec_ = std::move(ex);
 
     // One eager pass (lets kernels make their lazy, per-handle allocations outside a capture),
@@ -390,6 +457,10 @@ void SparseOnnxModel::launch_layers(const float* d_in, float* d_out, uint32_t B,
     auto src_of = [&](const std::string& name) -> const float* {
         return name == input_name_ ? d_in : ex.buf.at(name);
     };
+    // Fused exchange: a rank may store into a peer's buffer only after that peer has finished
+    // reading it in the previous pass, hence one barrier up front (all later layers are ordered by
+    // the barriers that follow each exchange).
+    if (ex.fused) check(spx_comm_barrier(comm_, stream), "barrier");
     for (const auto& L : layers_) {
         float* dst = L.outputs[0] == output_name_ ? d_out : ex.buf.at(L.outputs[0]);
         const float* src = src_of(L.inputs[0]);
@@ -399,6 +470,14 @@ void SparseOnnxModel::launch_layers(const float* d_in, float* d_out, uint32_t B,
             const uint64_t per = L.shard ? (L.E->m + world_ - 1) / world_ : 0;
             const uint64_t row0 = per * uint64_t(rank_);
             const float* bias = L.bias.empty() ? nullptr : ex.d_bias + L.bias_offset + (L.shard ? row0 : 0);
+            auto pit = ex.fused && L.shard ? ex.peers.find(L.outputs[0]) : ex.peers.end();
+            if (pit != ex.peers.end() && dst == ex.buf.at(L.outputs[0])) {
+                // epilogue stores this rank's rows into every rank's full buffer over NVLink
+                check(spx_spmm_bcast(E.dev, src, B, B, bias, L.act, pit->second.data(), uint32_t(world_), row0, B, stream),
+                      "MatMul layer (fused exchange)");
+                check(spx_comm_barrier(comm_, stream), "barrier");
+                break;
+            }
             check(spx_spmm(E.dev, src, B, B, bias, L.act, dst + row0 * B, B, stream), "MatMul layer");
             if (L.shard) check(spx_allgather_rows(comm_, dst, per, B, stream), "all-gather");
             break;

@@ -79,7 +79,10 @@ public:
     /// (Re)allocate the activation buffers for batch B and capture the layer loop as a CUDA graph.
     void resize_buffers(uint32_t B);
     /// Tensor-parallel mode: every MatMul / Conv keeps only rows [rank*ceil(m/world), ...) on this
-    /// process's GPU and each layer ends with an in-place NCCL all-gather of the row slabs.
+    /// process's GPU.  MatMul layers store their rows straight into every rank's full output buffer
+    /// (peers' buffers mapped over IPC, plain stores over NVLink, then a barrier); Conv layers, and
+    /// MatMul layers when the buffers cannot be shared (or SPX_TP_FUSED=0), end with an in-place NCCL
+    /// all-gather of the row slabs.
     /// unique_id: SPX_UNIQUE_ID_BYTES bytes from spx_comm_unique_id, identical on all ranks.
     void shard_rows(int rank, int world, const char* unique_id);
 
@@ -94,6 +97,7 @@ public:
 private:
     struct Exec;                                   // device buffers, stream, graph (mutable state)
     void build_exec(uint32_t B) const;
+    bool exchange_peer_buffers(Exec& ex, const std::vector<std::string>& names) const;
     void launch_layers(const float* d_in, float* d_out, uint32_t B, void* stream) const;
 
     std::vector<Layer> layers_;
