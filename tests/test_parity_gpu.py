@@ -445,3 +445,41 @@ def test_spmv_reference_order_is_bit_exact(lib, orc, golden, cuda, name):
     lib.spx_spmv_reference_order(h2.h, dx2.data_ptr(), db2.data_ptr(), dy.data_ptr(), 0)
     torch.cuda.synchronize()
     assert_bit_equal(dy.cpu().numpy(), orc.spmv(E2, x, b), "reference-order spmv vs oracle")
+
+
+def test_abi_rejects_misuse_with_status_codes(lib, orc, cuda):
+    """Failures are made on the host: every bad call returns a status and a message, nothing is
+    launched, and the context stays usable afterwards."""
+    import ctypes as C
+    E = orc.encode(np.eye(8, dtype=np.float32))
+    h = gpu_ell(lib, E)
+    x = torch.ones(8, device=cuda)
+    y = torch.zeros(8, device=cuda)
+    before = lib.spx_launch_count()
+    arr9 = (C.c_void_p * 9)(*([y.data_ptr()] * 9))
+    for call in (
+        lambda: lib.spx_spmm(h.h, x.data_ptr(), 1, 1, 0, 7, y.data_ptr(), 1, 0),                   # unknown activation
+        lambda: lib.spx_spmm(0, x.data_ptr(), 1, 1, 0, 0, y.data_ptr(), 1, 0),                     # null handle
+        lambda: lib.spx_spmm(h.h, x.data_ptr(), 1, 1, 0, 0, 0, 1, 0),                              # null output
+        lambda: lib.spx_spmv(h.h, 0, 0, y.data_ptr(), 0),                                          # null x with nonzeros
+        lambda: lib.spx_spmm_bcast(h.h, x.data_ptr(), 1, 1, 0, 0, arr9, 9, 0, 1, 0),               # more than 8 buffers
+        lambda: lib.spx_spmm_bcast(h.h, x.data_ptr(), 1, 1, 0, 0, None, 1, 0, 1, 0),               # null list
+        lambda: lib.spx_eltwise(9, x.data_ptr(), 0, y.data_ptr(), 8, 0),                           # unknown op
+        lambda: lib.spx_eltwise(sx.OP_ADD, x.data_ptr(), 0, y.data_ptr(), 8, 0),                   # add without b
+        lambda: lib.spx_maxpool2d(x.data_ptr(), 1, 2, 2, 2, 3, 3, 1, 1, 0, 0, 0, 0, y.data_ptr(), 0),   # window > input
+        lambda: lib.spx_comm_create(3, 2, b"\0" * 128, C.byref(C.c_void_p())),                     # rank >= world
+        lambda: lib.spx_allgather_rows(0, y.data_ptr(), 1, 1, 0),                                  # null communicator
+        lambda: lib.spx_ipc_export(0, C.create_string_buffer(64)),                                 # null pointer
+        lambda: lib.spx_graph_capture_begin(0),                                                    # default stream
+        lambda: lib.spx_ell_create_csr(2, 4, np.array([0, 2, 1], np.uint64).ctypes.data_as(C.c_void_p), 0, 0, C.byref(C.c_void_p())),
+    ):
+        with pytest.raises(sx.SpxError) as info:
+            call()
+        assert info.value.status in (1, 2, 4, 5) and str(info.value)
+    assert lib.spx_launch_count() == before
+    # unsorted CSR columns are refused too
+    with pytest.raises(sx.SpxError, match="ascending"):
+        lib.ell_create_csr(1, 4, np.array([0, 2], np.uint64), np.array([3, 1], np.uint32), np.ones(2, np.float32))
+    h.spmv(x.data_ptr(), 0, y.data_ptr())              # still works
+    torch.cuda.synchronize()
+    assert y.cpu().numpy().tolist() == [1.0] * 8
