@@ -225,7 +225,9 @@ def spmv_bytes(nnz, m, n):
 # ------------------------------------------------------------------------------------------------
 def cpu_engine():
     """(engine, kind): the unmodified reference build when usable here, else the C port."""
-    os.environ.setdefault("OMP_NUM_THREADS", str(host_cores()))
+    # all host cores, also under torchrun, which presets OMP_NUM_THREADS=1 for every rank (the
+    # reference reads the variable on every call)
+    os.environ["OMP_NUM_THREADS"] = str(host_cores())
     os.environ.setdefault("OMP_PLACES", "cores")
     os.environ.setdefault("OMP_PROC_BIND", "spread")
     import oracle
