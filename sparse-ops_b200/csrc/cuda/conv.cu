@@ -123,19 +123,20 @@ transpose2d_kernel(const float* __restrict__ src, uint64_t rows, uint64_t cols, 
 // ---------------------------------------------------------------------------------------------
 // conv_pf_tile_kernel: the fast path for the [C,H,W,B] layout with B % 4 == 0.
 //
-// A CTA owns a tile of 4 x 8 (2 x 8 at a full batch tile) output positions x BT batch entries x 16
-// (32) output channels (one warp per output channel, accumulators in registers for the whole kernel).  It walks the input
-// channels in chunks: the chunk's input patch (CC channels x the tile's receptive field x BT) is
+// A CTA owns a tile of 4 x 8 (2 x 8 at a full batch tile of 32) output positions x BT batch entries
+// x 16 (32) output channels: one warp per output channel, accumulators in registers for the whole
+// kernel.  It walks the input channels in chunks: the chunk's input patch (CC channels x the tile's receptive field x BT) is
 // staged in shared memory with 16-byte cp.async copies, positions outside the image are stored as
 // zeros (so a tap there contributes the operand 0.0f exactly like the reference's zero-filled
 // im2col tile), and every warp then consumes the nonzeros of its weight row whose input channel
 // lies in the chunk -- they are contiguous because rows are sorted by k = (cin, kh, kw).
 // Per nonzero: (w, tap offset) are read coalesced 32 at a time and broadcast with two shuffles,
-// then QB float4 shared-memory loads feed 4*QB FMAs per lane.  A quarter-warp always reads 128
+// then G float4 shared-memory loads feed 4*G FMAs per lane.  A quarter-warp always reads 128
 // contiguous bytes, so the loads are bank-conflict free for stride 1.
 //
 // Bound: one 4-byte operand per FMA from shared memory = 128 B/clk/SM = 32 FMA/clk/SM, a quarter
-// of the FP32 peak; HBM traffic is the input once per 16 output channels plus the output once.
+// of the FP32 peak; HBM / L2 traffic is the input patch once per CTA (16 or 32 output channels)
+// plus the output once.
 // ---------------------------------------------------------------------------------------------
 constexpr int kTileH = 4, kTileW = 8, kTileWarps = 16;
 
