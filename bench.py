@@ -15,7 +15,8 @@ input.  Workloads (the five benchmark configurations):
   cfg2_spmv             square iid matrix, --size in {4096,16384,65536}, --sparsity.
   cfg3_mlp              sparse MLP 4096-4096-4096-4096-1000, batch 256, via SparseOnnxModel
                         (N > 1: batch-sharded, no collective; --tp: row-sharded + all-gather).
-  cfg4_conv             sparse 3x3 conv 256->256, 56x56, batch 32, [C,H,W,B] layout.
+  cfg4_conv             sparse 3x3 conv 256->256, 56x56, batch 32, [C,H,W,B] layout (--nchw: NCHW).
+  cfg4_stack            four such layers chained, through SparseOnnxModel.
 
 `value` is measured with operands resident in HBM; `e2e` is the same metric through the
 host-buffer entry points (pinned host memory, copies inside the timed region).
@@ -50,7 +51,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg5_spmm",
-                    choices=["cfg5_spmm", "cfg1_spmm", "cfg1_spmv", "cfg2_spmv", "cfg3_mlp", "cfg4_conv"])
+                    choices=["cfg5_spmm", "cfg1_spmm", "cfg1_spmv", "cfg2_spmv", "cfg3_mlp", "cfg4_conv", "cfg4_stack"])
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (testing only)")
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
@@ -209,6 +210,9 @@ def build_workload(args, rank: int, world: int):
     if w == "cfg4_conv":
         d = wl.cfg4(s, layers=1)
         return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, " + ("NCHW" if args.nchw else "[C,H,W,B]"))
+    if w == "cfg4_stack":
+        d = wl.cfg4(s, layers=4)
+        return dict(kind="convstack", **d, desc=f"4 x (sparse conv {d['C']}->{d['C']} 3x3 + bias + ReLU) on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, via SparseOnnxModel, [C,H,W,B]")
     raise SystemExit(f"unknown workload {w}")
 
 
@@ -315,6 +319,28 @@ def cpu_sample_runner(args, wk, budget_rows=None):
                 f"{Bs} of {B} images, conv2d_patchmajor_tiled of the reference"
         E = eng.encode(wk["weights"][0].reshape(Cc, -1))
         return (lambda: eng.conv2d(E, g, 0, x_pf, Bs, wk["biases"][0], 1)), Bs / B, kind, f"{Bs} of {B} images, C port"
+    if wk["kind"] == "convstack":
+        import onnx_wire
+        import tempfile
+        B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
+        Bs = max(1, min(B, 2))
+        x_pf = np.ascontiguousarray(wk["x_nchw"][:Bs].transpose(1, 2, 3, 0))
+        if is_ref:
+            f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+            f.write(onnx_wire.conv_model(wk["weights"], wk["biases"], [True] * len(wk["weights"]), Bs, H, W))
+            f.close()
+            h = eng.model_load(f.name)
+            os.unlink(f.name)
+            return (lambda: eng.model_run(h, x_pf, Bs)), Bs / B, kind, f"{Bs} of {B} images, SparseOnnxModel::run of the reference"
+        g = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+        Es = [eng.encode(w.reshape(Cc, -1)) for w in wk["weights"]]
+
+        def run():
+            a = x_pf
+            for E, b in zip(Es, wk["biases"]):
+                a = eng.conv2d(E, g, 0, a, Bs, b, 1)
+            return a
+        return run, Bs / B, kind, f"{Bs} of {B} images, C port"
     raise SystemExit("no CPU sample for this workload")
 
 
@@ -334,7 +360,8 @@ def time_cpu(run, repeats, warmup=1, budget_s=25.0):
 
 def metric_of(wk, args):
     return {"spmm": ("spmm_effective_hbm_gbs", "GB/s"), "spmv": ("spmv_effective_hbm_gbs", "GB/s"),
-            "mlp": ("sparse_mlp_samples_per_s", "samples/s"), "conv": ("conv_effective_hbm_gbs", "GB/s")}[wk["kind"]]
+            "mlp": ("sparse_mlp_samples_per_s", "samples/s"), "conv": ("conv_effective_hbm_gbs", "GB/s"),
+            "convstack": ("conv_effective_hbm_gbs", "GB/s")}[wk["kind"]]
 
 
 def job_bytes_flops(wk, nnz_total):
@@ -356,6 +383,14 @@ def job_bytes_flops(wk, nnz_total):
         z = int(np.count_nonzero(wk["weights"][0]))
         cols = wk["B"] * wk["H"] * wk["W"]
         return 4 * cols * 2 * wk["C"] + 8 * z + 8 * wk["C"], 2.0 * z * cols
+    if k == "convstack":
+        cols = wk["B"] * wk["H"] * wk["W"]
+        by, fl = 0, 0.0
+        for w_ in wk["weights"]:
+            z = int(np.count_nonzero(w_))
+            by += 4 * cols * 2 * wk["C"] + 8 * z + 8 * wk["C"]
+            fl += 2.0 * z * cols
+        return by, fl
     raise SystemExit(k)
 
 
@@ -563,6 +598,35 @@ def measure(args, c):
             model.run(hX.numpy().reshape(Bl, -1))
         working_set = 64 << 20
         kernel_name = "spmm"
+    elif kind == "convstack":
+        import tempfile
+
+        import onnx_wire
+        import sparseops_backend as sb
+        sb.set_device(local)
+        B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
+        Bl = B // world
+        f = tempfile.NamedTemporaryFile(suffix=".onnx", delete=False)
+        f.write(onnx_wire.conv_model(wk["weights"], wk["biases"], [True] * len(wk["weights"]), Bl, H, W))
+        f.close()
+        model = sb.SparseOnnxModel(f.name)
+        os.unlink(f.name)
+        nnz_total = 0
+        x_pf = np.ascontiguousarray(wk["x_nchw"][rank * Bl:(rank + 1) * Bl].transpose(1, 2, 3, 0))
+        model.resize_buffers(Bl)
+        dX = torch.from_numpy(x_pf).to(dev)
+        lib.spx_memcpy_d2d(model.device_input_ptr(), dX.data_ptr(), dX.numel() * 4, stream)
+        torch.cuda.synchronize()
+
+        def step():
+            model.run_resident(stream)
+        hX = torch.from_numpy(x_pf).pin_memory()
+        h2d, d2h = hX.numel() * 4, model.out_features * Bl * 4
+
+        def e2e_step():
+            model.run(hX.numpy().reshape(Bl, Cc, H, W))
+        working_set = 64 << 20
+        kernel_name = "conv"
     elif kind == "conv":
         B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
         import sparseops_backend as sb
@@ -706,7 +770,7 @@ def measure(args, c):
         }
         # SpMM and conv move one 4-byte operand per FMA through the L2 -> SM gather path / shared
         # memory; that path, not HBM, is what their time tracks, so it is reported too.
-        if kind in ("spmm", "conv", "mlp"):
+        if kind in ("spmm", "conv", "convstack", "mlp"):
             op_bytes = job_flops / 2.0 * 4.0 / world
             line["roofline"]["operand_path"] = {
                 "what": "gathered X operands, 4 bytes per FMA (L2->SM for SpMM/MLP, shared memory for conv)",

@@ -249,3 +249,21 @@ def test_model_full_config3_vs_oracle(backend, orc, cuda):
     backend.ellpack_matmul_device(E, dX.data_ptr(), 256, 256, dB.data_ptr(), 1, dY.data_ptr(), 256)
     torch.cuda.synchronize()
     assert_bit_equal(dY.cpu().numpy(), orc.spmm(orc.encode(d["weights"][0]), x_mem, d["biases"][0], act=1), "layer 1")
+
+
+def test_model_conv_stack_config4_scaled_vs_oracle(backend, orc, cuda):
+    """The 4-layer conv + bias + ReLU stack of config 4 at a quarter of its size, through
+    SparseOnnxModel.run in [C,H,W,B] memory, bit-identical to the oracle layer by layer."""
+    import onnx_wire
+    import workloads as wl
+    d = wl.cfg4(0.25, layers=4)
+    B, Cc, H, W = d["B"], d["C"], d["H"], d["W"]
+    m = _load(backend, onnx_wire.conv_model(d["weights"], d["biases"], [True] * 4, B, H, W))
+    assert [l["op"] for l in m.layer_summary()] == ["Conv"] * 4 and all(l["act"] == 1 for l in m.layer_summary())
+    x_pf = np.ascontiguousarray(d["x_nchw"].transpose(1, 2, 3, 0))
+    y = m.run(x_pf.reshape(B, Cc, H, W)).ravel().reshape(Cc, H, W, B)
+    g = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+    a = x_pf
+    for wgt, b in zip(d["weights"], d["biases"]):
+        a = orc.conv2d(orc.encode(wgt.reshape(Cc, -1)), g, 0, a, B, b, 1)
+    assert_bit_equal(y, a, "conv stack")
