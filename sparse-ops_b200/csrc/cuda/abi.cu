@@ -210,32 +210,57 @@ int spx_event_elapsed_ms(void* start, void* stop, float* ms)
 }
 
 // ---- graphs --------------------------------------------------------------------------------
+// A captured graph remembers how many of this library's kernels it holds, so that replays keep
+// spx_launch_count() truthful.
+namespace {
+struct GraphExec {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
+};
+thread_local uint64_t t_capture_start = 0;
+}  // namespace
+
 int spx_graph_capture_begin(void* stream)
 {
     if (!stream) return fail(SPX_ERR_ARG, "graph capture needs a non-default stream");
     SPX_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    t_capture_start = g_launches.load(std::memory_order_relaxed);
     return SPX_OK;
 }
 int spx_graph_capture_end(void* stream, void** graph_exec)
 {
     if (!graph_exec) return fail(SPX_ERR_ARG, "graph_exec is null");
+    const uint64_t captured = g_launches.load(std::memory_order_relaxed) - t_capture_start;
+    // launches made while capturing were recorded, not run: take them out of the running count
+    g_launches.fetch_sub(captured, std::memory_order_relaxed);
     cudaGraph_t g = nullptr;
     SPX_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
     cudaGraphExec_t ge = nullptr;
     cudaError_t err = cudaGraphInstantiate(&ge, g, 0);
     cudaGraphDestroy(g);
     if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(err));
-    *graph_exec = ge;
+    GraphExec* h = new (std::nothrow) GraphExec();
+    if (!h) { cudaGraphExecDestroy(ge); return fail(SPX_ERR_OOM, "out of host memory"); }
+    h->exec = ge;
+    h->kernels = captured;
+    *graph_exec = h;
     return SPX_OK;
 }
 int spx_graph_launch(void* graph_exec, void* stream)
 {
-    SPX_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, (cudaStream_t)stream));
+    if (!graph_exec) return fail(SPX_ERR_ARG, "graph_exec is null");
+    GraphExec* h = static_cast<GraphExec*>(graph_exec);
+    SPX_CUDA(cudaGraphLaunch(h->exec, (cudaStream_t)stream));
+    count_launch(h->kernels);
     return SPX_OK;
 }
 int spx_graph_destroy(void* graph_exec)
 {
-    if (graph_exec) SPX_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+    if (!graph_exec) return SPX_OK;
+    GraphExec* h = static_cast<GraphExec*>(graph_exec);
+    cudaError_t err = cudaGraphExecDestroy(h->exec);
+    delete h;
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "cudaGraphExecDestroy failed: %s", cudaGetErrorString(err));
     return SPX_OK;
 }
 

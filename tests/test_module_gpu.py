@@ -164,7 +164,9 @@ def test_model_resize_and_device_run(backend, golden, orc, cuda):
     import spx_ctypes as sx
     sx.Lib().spx_memcpy_d2d(m.device_input_ptr(), dX2.data_ptr(), n_in, 0)
     torch.cuda.synchronize()
+    before = backend.launch_count()
     m.run_resident(0)
+    assert backend.launch_count() == before + 2          # graph replays count their kernels (two fused layers)
     out = torch.empty(want.shape, device=cuda)
     sx.Lib().spx_memcpy_d2d(out.data_ptr(), m.device_output_ptr(), out.numel() * 4, 0)
     torch.cuda.synchronize()
