@@ -47,7 +47,7 @@ template <class T>
 static py::array_t<T> copy2d(const T* src, uint32_t m, uint32_t r)
 {
     py::array_t<T> a({ py::ssize_t(m), py::ssize_t(r) });
-    if (size_t(m) * r) std::memcpy(a.mutable_data(), src, size_t(m) * r * sizeof(T));
+    if (m && r) std::memcpy(a.mutable_data(), src, size_t(m) * r * sizeof(T));
     return a;
 }
 

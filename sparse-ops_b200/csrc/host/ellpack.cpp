@@ -64,7 +64,7 @@ Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G, bool do_upload) const
     const uint32_t per = (m + G - 1) / G;
     const uint32_t lo = std::min(m, g * per), hi = std::min(m, lo + per);
     Ellpack S(hi - lo, n, r);
-    if (size_t(S.m) * r) {
+    if (S.m && r) {
         std::memcpy(S.Wd.ptr, Wd.ptr + size_t(lo) * r, size_t(S.m) * r * sizeof(float));
         std::memcpy(S.idx.data(), idx.data() + size_t(lo) * r, size_t(S.m) * r * sizeof(uint32_t));
     }
@@ -112,7 +112,7 @@ Ellpack encode_host(const float* W, uint32_t m, uint32_t n)
     for (uint32_t c : counts) r = std::max(r, c);
     Ellpack E(m, n, r);
     E.nnz = std::move(counts);
-    if (size_t(m) * r) std::memset(E.Wd.ptr, 0, size_t(m) * r * sizeof(float));
+    if (m && r) std::memset(E.Wd.ptr, 0, size_t(m) * r * sizeof(float));
     parallel_rows(m, n, [&](uint32_t lo, uint32_t hi) {
         for (uint32_t i = lo; i < hi; ++i) {
             const float* row = W + size_t(i) * n;
@@ -147,7 +147,7 @@ Ellpack ellpack_from_csr(uint32_t m, uint32_t n, const uint64_t* rowptr, const u
         r = std::max<uint64_t>(r, rowptr[i + 1] - rowptr[i]);
     }
     Ellpack E(m, n, r);
-    if (size_t(m) * r) std::memset(E.Wd.ptr, 0, size_t(m) * r * sizeof(float));
+    if (m && r) std::memset(E.Wd.ptr, 0, size_t(m) * r * sizeof(float));
     for (uint32_t i = 0; i < m; ++i) {
         const uint64_t b = rowptr[i], c = rowptr[i + 1] - b;
         E.nnz[i] = uint32_t(c);

@@ -243,7 +243,6 @@ SparseOnnxModel::SparseOnnxModel(const std::string& onnx_path, bool upload_weigh
             for (size_t d = 1; d < in_shape.size(); ++d) prod *= in_shape[d];
             name_alias_[out] = in;
             shape_map_[out] = { in_shape[0], prod };
-            flat_shape_[in] = shape_map_[out];
             continue;
         }
 

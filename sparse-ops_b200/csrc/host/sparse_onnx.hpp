@@ -107,7 +107,6 @@ private:
     std::vector<int> input_shape_;
     std::unordered_map<std::string, std::vector<int>> shape_map_;
     std::unordered_map<std::string, std::string> name_alias_;
-    std::unordered_map<std::string, std::vector<int>> flat_shape_;
     std::vector<int> output_label_shape_;
     std::string input_name_, output_name_;
     int rank_ = 0, world_ = 1;
