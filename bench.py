@@ -56,7 +56,7 @@ def parse_args():
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
     ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
-    ap.add_argument("--batch", type=int, default=0, help="cfg3_mlp: override the batch size")
+    ap.add_argument("--batch", type=int, default=0, help="cfg3_mlp / cfg4_conv: override the batch size")
     ap.add_argument("--nchw", action="store_true", help="cfg4_conv: NCHW tensors instead of [C,H,W,B]")
     ap.add_argument("--rows", type=int, default=0, help="cfg5_spmm: override the row count (profiling on a smaller case)")
     ap.add_argument("--cols", type=int, default=0, help="cfg5_spmm: override C, the dense column count")
@@ -209,6 +209,9 @@ def build_workload(args, rank: int, world: int):
         return dict(kind="mlp", **d, desc=f"sparse MLP {'-'.join(map(str, d['dims']))}, 90% sparse, batch {d['B']}")
     if w == "cfg4_conv":
         d = wl.cfg4(s, layers=1)
+        if args.batch:
+            d["x_nchw"] = np.ascontiguousarray(d["x_nchw"][:args.batch])
+            d["B"] = d["x_nchw"].shape[0]
         return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, " + ("NCHW" if args.nchw else "[C,H,W,B]"))
     if w == "cfg4_stack":
         d = wl.cfg4(s, layers=4)

@@ -334,7 +334,14 @@ static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const floa
     // 256 -> 256 channels, 56 x 56, batch 32: 1.89 ms against 2.03 ms.  SPX_CONV_SMALL_TILE=0 selects
     // the larger tile.
     const bool small = BT == 32 && small_tile != 0;
-    const uint32_t TH = small ? 2 : kTileH;
+    // Batch tile of 8 entries: a 4 x 8 tile would leave a lane two float4 per nonzero, so the warp
+    // takes 8 x 8 positions instead and the two broadcast shuffles per nonzero are amortised over 4
+    // shared-memory loads (0.571 ms against 0.593 ms on 256 -> 256 channels, 56 x 56, batch 8; a
+    // 16 x 8 tile for 4 entries measured slower than 4 x 8).  SPX_CONV_WIDE_TILE=0 turns it off.
+    static const int wide_env = [] { const char* v = getenv("SPX_CONV_WIDE_TILE"); return v ? atoi(v) : 1; }();
+    const uint32_t QBv = BT / 4;
+    const uint32_t Gv = (wide_env && QBv == 2) ? 4 : (small ? 4 : QBv);
+    const uint32_t TH = 32 * Gv / QBv / kTileW;
     const uint32_t warps = small ? 32 : kTileWarps;
     TileParams tp{};
     tp.c = p;
@@ -357,6 +364,7 @@ static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const floa
     dim3 grid((unsigned)tiles, gy, gz);
     const size_t smem = chanBytes * tp.CC;
     if (small) return launch_tile_qb<8, 4, 32, 1>(e, tp, grid, smem, in, bias, act, out, s);
+    if (Gv != QBv) return launch_tile_qb<2, 4, kTileWarps, 2>(e, tp, grid, smem, in, bias, act, out, s);
 #define SPX_TILE_CASE(Q)                                                                                           \
     case Q: return per_sm == 2 ? launch_tile_qb<Q, Q, kTileWarps, 2>(e, tp, grid, smem, in, bias, act, out, s)     \
                                : launch_tile_qb<Q, Q, kTileWarps, 1>(e, tp, grid, smem, in, bias, act, out, s);
