@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (testing only)")
     ap.add_argument("--size", type=int, default=16384, help="cfg2_spmv: m = n")
     ap.add_argument("--sparsity", type=float, default=0.90, help="cfg2_spmv")
+    ap.add_argument("--conv-sparsity", type=float, default=0.80, help="cfg4_conv: fraction of zero weights")
     ap.add_argument("--tp", action="store_true", help="cfg3_mlp at N > 1: row-sharded layers + all-gather")
     ap.add_argument("--batch", type=int, default=0, help="cfg3_mlp / cfg4_conv: override the batch size")
     ap.add_argument("--nchw", action="store_true", help="cfg4_conv: NCHW tensors instead of [C,H,W,B]")
@@ -208,11 +209,11 @@ def build_workload(args, rank: int, world: int):
         d = wl.cfg3(s, batch=args.batch or None)
         return dict(kind="mlp", **d, desc=f"sparse MLP {'-'.join(map(str, d['dims']))}, 90% sparse, batch {d['B']}")
     if w == "cfg4_conv":
-        d = wl.cfg4(s, layers=1)
+        d = wl.cfg4(s, layers=1, density=1.0 - args.conv_sparsity)
         if args.batch:
             d["x_nchw"] = np.ascontiguousarray(d["x_nchw"][:args.batch])
             d["B"] = d["x_nchw"].shape[0]
-        return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, bias+ReLU, " + ("NCHW" if args.nchw else "[C,H,W,B]"))
+        return dict(kind="conv", **d, desc=f"sparse conv {d['C']}->{d['C']} 3x3 on {d['H']}x{d['W']}, batch {d['B']}, {args.conv_sparsity:.0%} sparse, bias+ReLU, " + ("NCHW" if args.nchw else "[C,H,W,B]"))
     if w == "cfg4_stack":
         d = wl.cfg4(s, layers=4)
         return dict(kind="convstack", **d, desc=f"4 x (sparse conv {d['C']}->{d['C']} 3x3 + bias + ReLU) on {d['H']}x{d['W']}, batch {d['B']}, 80% sparse, via SparseOnnxModel, [C,H,W,B]")
@@ -776,7 +777,9 @@ def measure(args, c):
         if kind in ("spmm", "conv", "convstack", "mlp"):
             op_bytes = job_flops / 2.0 * 4.0 / world
             line["roofline"]["operand_path"] = {
-                "what": "gathered X operands, 4 bytes per FMA (L2->SM for SpMM/MLP, shared memory for conv)",
+                "what": "X operands consumed, 4 bytes per FMA (gathered L2->SM for SpMM/MLP; for conv read from "
+                        "shared memory, once per FMA by the per-row kernel, once per block of 4 rows by the "
+                        "row-block-merged kernel)",
                 "bytes_per_step": op_bytes, "achieved_tbps": op_bytes / sec / 1e12}
         if e2e:
             line["e2e"] = e2e

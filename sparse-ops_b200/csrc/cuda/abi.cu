@@ -276,12 +276,15 @@ int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const ui
     // be a valid row of X, every count must fit the slab.
     uint64_t total = 0;
     uint32_t longest = 0;
+    bool ascending = true;
     for (uint32_t i = 0; i < m; ++i) {
         const uint32_t c = nnz[i];
         if (c > r) return fail(SPX_ERR_ARG, "nnz[%u] = %u exceeds r = %u", i, c, r);
         const uint32_t* row = idx + (size_t)i * r;
-        for (uint32_t j = 0; j < c; ++j)
+        for (uint32_t j = 0; j < c; ++j) {
             if (row[j] >= n) return fail(SPX_ERR_ARG, "idx[%u,%u] = %u is not below n = %u", i, j, row[j], n);
+            if (j && row[j] <= row[j - 1]) ascending = false;
+        }
         total += c;
         if (c > longest) longest = c;
     }
@@ -290,6 +293,7 @@ int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const ui
     if (rc != SPX_OK) return rc;
     e->nnz_total = total;
     e->max_nnz = longest;
+    e->cols_ascending = ascending;
     cudaError_t err = cudaSuccess;
     if ((size_t)m * r) {
         err = cudaMemcpy2D(e->Wd, (size_t)e->pitch * 4, Wd, (size_t)r * 4, (size_t)r * 4, m, cudaMemcpyHostToDevice);
@@ -373,7 +377,7 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
-    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
     for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
     delete e;
     return SPX_OK;

@@ -31,6 +31,18 @@ struct spx_ell {
     // kernel shape (conv.cu); keyed by (kH, kW).
     uint32_t* taps = nullptr;
     uint32_t taps_kH = 0, taps_kW = 0;
+    // True when every row's stored column ids are strictly ascending (always so for handles made
+    // from CSR, from a dense matrix or by the encoders; checked at upload for raw arrays).  The
+    // tiled convolution kernels rely on it; without it the convolution takes the general kernel.
+    bool cols_ascending = true;
+    // Lazily built row-block-merged form of the weights for the convolution (conv.cu): per block
+    // of 4 rows the ascending union of their column ids; per union column a header
+    // (packed tap, 4-bit row mask) and the 4 rows' weights (0.0f where a row has no entry).
+    // Block b owns entries [b * rbm_cap, b * rbm_cap + rbm_ncols[b]).
+    uint2* rbm_hdr = nullptr;
+    float* rbm_w = nullptr;
+    uint32_t* rbm_ncols = nullptr;
+    uint32_t rbm_cap = 0, rbm_kH = 0, rbm_kW = 0;
     // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
     void* stage_dev = nullptr;
     size_t stage_dev_bytes = 0;

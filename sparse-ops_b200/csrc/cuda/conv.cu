@@ -15,6 +15,7 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 
 namespace {
@@ -154,6 +155,35 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
+// Stages input channels [c0, c1) of a CTA's receptive field in shared memory as
+// [channel][row][column][BT batch entries]: one warp per (channel, row), 16-byte cp.async copies,
+// zeros where the row or column lies outside the image.  Ends with the copies landed and the CTA
+// synchronised.
+template <int QB, int WARPS>
+__device__ __forceinline__ void stage_chunk(float* tile, const TileParams& tp, const float* __restrict__ in,
+                                            uint32_t c0, uint32_t c1, int ih0, int iw0, uint32_t b0,
+                                            int warp, int lane)
+{
+    const ConvParams& p = tp.c;
+    const uint32_t rowUnits = tp.TWin * QB;             // float4 units per staged row
+    const uint32_t rows = (c1 - c0) * tp.THin;
+    for (uint32_t r = warp; r < rows; r += WARPS) {
+        const uint32_t c = r / tp.THin, y = r % tp.THin;
+        const int ih = ih0 + (int)y;
+        const bool rowok = (unsigned)ih < p.H;
+        float* srow = tile + (size_t)r * rowUnits * 4;
+        const float* grow = in + (((size_t)(c0 + c) * p.H + (rowok ? ih : 0)) * p.W) * p.B + b0;
+        for (uint32_t u = lane; u < rowUnits; u += 32) {
+            const uint32_t x = u / QB, q = u % QB;
+            const int iw = iw0 + (int)x;
+            if (rowok && (unsigned)iw < p.W) cp_async16(srow + u * 4, grow + (size_t)iw * p.B + q * 4);
+            else *reinterpret_cast<float4*>(srow + u * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+}
+
 // QB: batch quads per output position (= BT / 4); G: float4 groups per lane, so a warp covers
 // 32*G/QB positions (kTileW wide); WARPS: output channels per CTA; MINB: CTAs per SM aimed for.
 template <int QB, int G, int WARPS, int MINB>
@@ -175,7 +205,6 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
     const bool active = mo < p.Cout;
     const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;      // image row of staged row 0
     const int iw0 = (int)(ow0 * p.sW) - (int)p.pW;
-    const uint32_t rowUnits = tp.TWin * QB;             // float4 units per staged row
 
     // this lane's G output units: unit q = lane + 32 g -> (position, batch quad)
     uint32_t off[G];
@@ -198,23 +227,7 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
 
     for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC) {
         const uint32_t c1 = min(p.Cin, c0 + tp.CC);
-        // ---- stage the chunk: one warp per (channel, row) of the patch ----
-        const uint32_t rows = (c1 - c0) * tp.THin;
-        for (uint32_t r = warp; r < rows; r += WARPS) {
-            const uint32_t c = r / tp.THin, y = r % tp.THin;
-            const int ih = ih0 + (int)y;
-            const bool rowok = (unsigned)ih < p.H;
-            float* srow = tile + (size_t)r * rowUnits * 4;
-            const float* grow = in + (((size_t)(c0 + c) * p.H + (rowok ? ih : 0)) * p.W) * p.B + b0;
-            for (uint32_t u = lane; u < rowUnits; u += 32) {
-                const uint32_t x = u / QB, q = u % QB;
-                const int iw = iw0 + (int)x;
-                if (rowok && (unsigned)iw < p.W) cp_async16(srow + u * 4, grow + (size_t)iw * p.B + q * 4);
-                else *reinterpret_cast<float4*>(srow + u * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        cp_async_wait_all();
-        __syncthreads();
+        stage_chunk<QB, WARPS>(tile, tp, in, c0, c1, ih0, iw0, b0, warp, lane);
         // ---- consume this row's nonzeros whose input channel is in [c0, c1) ----
         if (active) {
             for (;;) {
@@ -258,6 +271,210 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
                 o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
             }
             *reinterpret_cast<float4*>(out + (((size_t)mo * p.Ho + oh) * p.Wo + ow) * p.B + b0 + quad * 4) = o;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row-block-merged weights.  The reference's build_rbm_from_ellpack (src/layers/rbm_conv.cpp:7-73)
+// merges the column ids of consecutive weight rows into one ascending list so that a patch
+// operand is fetched once per block of rows instead of once per row; its consumer
+// (conv2d_rbm_fmajor_implicit, src/layers/conv_kernels.cpp:66-147) is not called at its HEAD.
+// Here the same merge feeds the tiled kernel below, with blocks of 4 rows (8 rows, the
+// reference's block, measured slower at every density: twice the mask tests per union column).
+// Device form, per block b of 4 rows:
+//   hdr[b*cap + c] = (packed tap cin<<16 | kh<<8 | kw of union column c,  bit r set when row
+//                     4b + r stores that column)
+//   w[(b*cap + c)*4 + r] = that row's weight, 0.0f where the bit is clear (never multiplied)
+//   ncols[b] = number of union columns.
+// One CTA per block: a K-bit set in shared memory collects the columns, a scan over its words
+// ranks them, a second pass over the rows scatters taps, masks and weights.
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t kRbmRows = 4;
+constexpr uint32_t kRbmMaxK = 1u << 17;         // 2 x 16 KB of shared memory for the set and its ranks
+
+__global__ void __launch_bounds__(256)
+build_rbm_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx, const uint32_t* __restrict__ nnz,
+                 uint32_t m, uint32_t K, uint32_t pitch, uint32_t kH, uint32_t kW, uint32_t cap,
+                 uint2* __restrict__ hdr, float* __restrict__ w4, uint32_t* __restrict__ ncols)
+{
+    extern __shared__ uint32_t rbm_sm[];
+    const uint32_t words = (K + 31) / 32;
+    uint32_t* set = rbm_sm;
+    uint32_t* rank = rbm_sm + words;
+    __shared__ uint32_t total_s;
+    const uint32_t blk = blockIdx.x, r0 = blk * kRbmRows;
+    for (uint32_t i = threadIdx.x; i < words; i += blockDim.x) set[i] = 0;
+    __syncthreads();
+    for (uint32_t r = 0; r < kRbmRows && r0 + r < m; ++r) {
+        const uint32_t row = r0 + r, nn = nnz[row];
+        for (uint32_t j = threadIdx.x; j < nn; j += blockDim.x) {
+            const uint32_t k = idx[(size_t)row * pitch + j];
+            atomicOr(&set[k >> 5], 1u << (k & 31));
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {                     // exclusive scan of the words' popcounts, 32 at a time
+        uint32_t run = 0;
+        for (uint32_t w0 = 0; w0 < words; w0 += 32) {
+            const uint32_t i = w0 + threadIdx.x;
+            const uint32_t c = i < words ? __popc(set[i]) : 0u;
+            uint32_t inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)threadIdx.x >= o) inc += v;
+            }
+            if (i < words) rank[i] = run + inc - c;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (threadIdx.x == 0) { total_s = run; ncols[blk] = run; }
+    }
+    __syncthreads();
+    const uint32_t total = total_s;
+    const size_t base = (size_t)blk * cap;
+    for (uint32_t c = threadIdx.x; c < total; c += blockDim.x) hdr[base + c] = make_uint2(0u, 0u);
+    for (uint32_t c = threadIdx.x; c < total * kRbmRows; c += blockDim.x) w4[base * kRbmRows + c] = 0.0f;
+    __syncthreads();
+    for (uint32_t r = 0; r < kRbmRows && r0 + r < m; ++r) {
+        const uint32_t row = r0 + r, nn = nnz[row];
+        for (uint32_t j = threadIdx.x; j < nn; j += blockDim.x) {
+            const uint32_t k = idx[(size_t)row * pitch + j];
+            const uint32_t c = rank[k >> 5] + __popc(set[k >> 5] & ((1u << (k & 31)) - 1u));
+            const uint32_t kw = k % kW, kh = (k / kW) % kH, cin = k / (kW * kH);
+            hdr[base + c].x = (cin << 16) | (kh << 8) | kw;      // the same value from every row
+            atomicOr(&hdr[base + c].y, 1u << r);
+            w4[(base + c) * kRbmRows + r] = Wd[(size_t)row * pitch + j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// conv_rbm_tile_kernel: the tiled kernel over row-block-merged weights.
+//
+// Same CTA structure as conv_pf_tile_kernel (input chunk staged in shared memory, accumulators
+// in registers for the whole kernel), but a warp owns a block of 4 output channels x 128/QB
+// positions: per union column it loads its 4 float4 patch operands ONCE and applies them to
+// every row of the block that stores the column (mask bits tested with warp-uniform branches;
+// the row's weight is broadcast from the lane that preloaded the column).  Shared-memory loads
+// per FMA drop by the mean number of rows per union column (1.36 at 80 % sparsity, 2.1 at
+// 50 %, 4 for a dense weight), which is what bounds conv_pf_tile_kernel; the price is the mask
+// tests, so the kernel is issue-bound rather than shared-memory-bound.  A row still sees its
+// nonzeros in ascending k with one FMA each: results are bit-identical to the per-row kernels.
+// The CTA's NB warps are NB row blocks on one tile of positions.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRbmG = 4;                                 // float4 groups per lane: 4 rows x 4 groups = 64 accumulators
+
+// One row of the block: when the union column holds an entry of row R, fetch its weight from the
+// lane that preloaded the column and run the row's 16 FMAs.  The test is warp-uniform.
+template <int R>
+__device__ __forceinline__ void rbm_row(float4 (&acc)[kRbmRows][kRbmG], uint32_t hm, float wsrc, uint32_t t,
+                                        const float4 (&x)[kRbmG])
+{
+    if (hm & (1u << R)) {
+        const float wt = __shfl_sync(0xffffffffu, wsrc, t);
+#pragma unroll
+        for (int g = 0; g < kRbmG; ++g) {
+            acc[R][g].x = fmaf(wt, x[g].x, acc[R][g].x);
+            acc[R][g].y = fmaf(wt, x[g].y, acc[R][g].y);
+            acc[R][g].z = fmaf(wt, x[g].z, acc[R][g].z);
+            acc[R][g].w = fmaf(wt, x[g].w, acc[R][g].w);
+        }
+    }
+}
+
+template <int QB, int NB>
+__global__ void __launch_bounds__(NB * 32, 1)
+conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w4,
+                     const uint32_t* __restrict__ ncols, uint32_t cap, TileParams tp,
+                     const float* __restrict__ in, const float* __restrict__ bias, int act,
+                     float* __restrict__ out)
+{
+    extern __shared__ __align__(16) float tile[];
+    constexpr int G = kRbmG, RB = (int)kRbmRows;
+    constexpr uint32_t BT = QB * 4;
+    constexpr uint32_t TH = 32u * G / QB / kTileW;       // rows of output positions per tile
+    const ConvParams& p = tp.c;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t ty = blockIdx.x / tp.tilesX, tx = blockIdx.x % tp.tilesX;
+    const uint32_t oh0 = ty * TH, ow0 = tx * kTileW;
+    const uint32_t b0 = blockIdx.z * BT;
+    const uint32_t blk = blockIdx.y * NB + warp;
+    const uint32_t mo0 = blk * RB;
+    const bool active = mo0 < p.Cout;
+    const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;
+    const int iw0 = (int)(ow0 * p.sW) - (int)p.pW;
+
+    uint32_t off[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const uint32_t q = lane + 32u * g;
+        const uint32_t pix = q / QB, quad = q % QB;
+        off[g] = (((pix / kTileW) * p.sH) * tp.TWin + (pix % kTileW) * p.sW) * BT + quad * 4;
+    }
+    float4 acc[RB][G];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        const float bv = (bias && mo0 + r < p.Cout) ? __ldg(bias + mo0 + r) : 0.0f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[r][g] = make_float4(bv, bv, bv, bv);
+    }
+    const uint32_t nn = active ? __ldg(ncols + blk) : 0u;
+    const uint2* __restrict__ hrow = hdr + (size_t)(active ? blk : 0) * cap;
+    const float4* __restrict__ wrow = w4 + (size_t)(active ? blk : 0) * cap;
+    uint32_t pos = 0;
+
+    for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC) {
+        const uint32_t c1 = min(p.Cin, c0 + tp.CC);
+        stage_chunk<QB, NB>(tile, tp, in, c0, c1, ih0, iw0, b0, warp, lane);
+        if (active) {
+            for (;;) {
+                // lane l preloads union column pos + l: shared-memory offset << 8 | row mask, and its 4 weights
+                uint32_t hl = 0, cin = 0xffffffffu;
+                float4 wl = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (pos + lane < nn) {
+                    const uint2 h = __ldg(hrow + pos + lane);
+                    cin = h.x >> 16;
+                    const uint32_t tl = (((cin - c0) * tp.THin + ((h.x >> 8) & 0xffu) * p.dH) * tp.TWin + (h.x & 0xffu) * p.dW) * BT;
+                    hl = (tl << 8) | h.y;
+                    wl = __ldg(wrow + pos + lane);
+                }
+                const uint32_t cnt = __popc(__ballot_sync(0xffffffffu, cin < c1));   // a prefix: columns ascend
+                for (uint32_t t = 0; t < cnt; ++t) {
+                    const uint32_t hm = __shfl_sync(0xffffffffu, hl, t);
+                    const float* xs = tile + (hm >> 8);
+                    float4 x[G];
+#pragma unroll
+                    for (int g = 0; g < G; ++g) x[g] = *reinterpret_cast<const float4*>(xs + off[g]);
+                    rbm_row<0>(acc, hm, wl.x, t, x);
+                    rbm_row<1>(acc, hm, wl.y, t, x);
+                    rbm_row<2>(acc, hm, wl.z, t, x);
+                    rbm_row<3>(acc, hm, wl.w, t, x);
+                }
+                pos += cnt;
+                if (cnt < 32) break;
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        const uint32_t mo = mo0 + r;
+        if (mo >= p.Cout) break;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const uint32_t q = lane + 32u * g;
+            const uint32_t pix = q / QB, quad = q % QB;
+            const uint32_t oh = oh0 + pix / kTileW, ow = ow0 + pix % kTileW;
+            if (oh < p.Ho && ow < p.Wo) {
+                float4 o = acc[r][g];
+                if (act != SPX_ACT_NONE) {
+                    o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
+                    o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
+                }
+                *reinterpret_cast<float4*>(out + (((size_t)mo * p.Ho + oh) * p.Wo + ow) * p.B + b0 + quad * 4) = o;
+            }
         }
     }
 }
@@ -316,16 +533,101 @@ static int transpose2d(const float* src, uint64_t rows, uint64_t cols, float* ds
     return SPX_OK;
 }
 
+// Builds (once per handle and kernel shape) the row-block-merged weights.
+static int ensure_rbm(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
+{
+    if (e->rbm_hdr && e->rbm_kH == kH && e->rbm_kW == kW) return SPX_OK;
+    const uint32_t nblocks = (e->m + kRbmRows - 1) / kRbmRows;
+    if (!e->rbm_hdr) {
+        const uint32_t cap = (uint32_t)std::min<uint64_t>((uint64_t)kRbmRows * e->max_nnz, e->n);
+        SPX_CUDA(cudaMalloc(&e->rbm_ncols, (size_t)nblocks * sizeof(uint32_t)));
+        SPX_CUDA(cudaMalloc(&e->rbm_w, (size_t)nblocks * cap * kRbmRows * sizeof(float)));
+        SPX_CUDA(cudaMalloc(&e->rbm_hdr, (size_t)nblocks * cap * sizeof(uint2)));
+        e->rbm_cap = cap;
+    }
+    const size_t smem = (size_t)((e->n + 31) / 32) * 2 * sizeof(uint32_t);
+    build_rbm_kernel<<<nblocks, 256, smem, s>>>(e->Wd, e->idx, e->nnz, e->m, e->n, e->pitch, kH, kW, e->rbm_cap,
+                                                e->rbm_hdr, e->rbm_w, e->rbm_ncols);
+    SPX_LAUNCH_CHECK("build_rbm_kernel");
+    e->rbm_kH = kH;
+    e->rbm_kW = kW;
+    return SPX_OK;
+}
+
+template <int QB>
+static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float* bias, int act, float* out,
+                         cudaStream_t s)
+{
+    constexpr int NB = 16;
+    const ConvParams& p = tp.c;
+    constexpr uint32_t TH = 32u * kRbmG / QB / kTileW;
+    tp.BT = QB * 4;
+    tp.THin = (TH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
+    tp.TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
+    const size_t chanBytes = (size_t)tp.THin * tp.TWin * tp.BT * sizeof(float);
+    const size_t budget = 200 * 1024;
+    if (chanBytes > budget) return -1;
+    tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
+    tp.tilesX = (p.Wo + kTileW - 1) / kTileW;
+    const uint64_t tiles = (uint64_t)tp.tilesX * ((p.Ho + TH - 1) / TH);
+    const uint32_t nblocks = (p.Cout + kRbmRows - 1) / kRbmRows;
+    const uint32_t gy = (nblocks + NB - 1) / NB, gz = p.B / tp.BT;
+    if (tiles > 0x7fffffffull || gy > 65535 || gz > 65535) return -1;
+    const int rc = ensure_rbm(e, p.kH, p.kW, s);
+    if (rc != SPX_OK) return rc;
+    const size_t smem = chanBytes * tp.CC;
+    auto kfn = conv_rbm_tile_kernel<QB, NB>;
+    cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    kfn<<<dim3((unsigned)tiles, gy, gz), NB * 32, smem, s>>>(e->rbm_hdr, reinterpret_cast<const float4*>(e->rbm_w),
+                                                           e->rbm_ncols, e->rbm_cap, tp, in, bias, act, out);
+    SPX_LAUNCH_CHECK("conv_rbm_tile_kernel");
+    return SPX_OK;
+}
+
+// Row-block-merged path.  Taken when K fits the builder's set and the expected number of rows per
+// union column, 4 d / (1 - (1 - d)^4) for density d, pays for the mask tests.  Measured against
+// conv_pf_tile_kernel on 256 -> 256 channels, 3 x 3, 56 x 56:
+//   batch a multiple of 16: tiles of 16 entries (faster than 32: twice the channels per staged
+//     chunk); wins from 80 % sparsity down (1.83 vs 1.89 ms at 80 %, 2.93 vs 4.15 ms at 50 %,
+//     4.1 vs 7.9 ms dense), loses at 90 % -> share >= 1.3;
+//   batch tile of 8: wins at 50 % (1.02 vs 1.16 ms), loses at 80 % -> share >= 1.7;
+//   batch tile of 4: wins at every density tried (0.26 vs 0.37 ms at 90 %).
+// Other batch sizes keep the per-row kernel with its wider batch tile.  SPX_CONV_RBM=0 turns the
+// path off, SPX_CONV_RBM_MIN_SHARE overrides the three thresholds.  Returns -1 when not taken.
+static int launch_conv_rbm_tile(spx_ell* e, const ConvParams& p, uint32_t BT, const float* in, const float* bias,
+                                int act, float* out, cudaStream_t s)
+{
+    static const int enabled = [] { const char* v = getenv("SPX_CONV_RBM"); return v ? atoi(v) : 1; }();
+    static const double share_env = [] { const char* v = getenv("SPX_CONV_RBM_MIN_SHARE"); return v ? atof(v) : -1.0; }();
+    if (!enabled || e->n > kRbmMaxK || e->m < kRbmRows || e->max_nnz == 0) return -1;
+    const uint32_t bt = p.B % 16 == 0 ? 16 : BT;       // BT: the per-row kernel's batch tile for this batch
+    if (bt != 16 && bt != 8 && bt != 4) return -1;
+    const double d = (double)e->nnz_total / ((double)e->m * e->n);
+    const double share = d >= 1.0 ? (double)kRbmRows : kRbmRows * d / (1.0 - std::pow(1.0 - d, (double)kRbmRows));
+    const double min_share = share_env >= 0.0 ? share_env : bt == 16 ? 1.3 : bt == 8 ? 1.7 : 1.0;
+    if (share < min_share) return -1;
+    TileParams tp{};
+    tp.c = p;
+    if (bt == 16) return launch_rbm_qb<4>(e, tp, in, bias, act, out, s);
+    if (bt == 8) return launch_rbm_qb<2>(e, tp, in, bias, act, out, s);
+    return launch_rbm_qb<1>(e, tp, in, bias, act, out, s);
+}
+
 // Returns -1 when the shape is not covered (caller falls back to the direct kernel).
-static int launch_conv_pf_tile(const spx_ell* e, const ConvParams& p, const float* in, const float* bias, int act,
+static int launch_conv_pf_tile(spx_ell* e, const ConvParams& p, const float* in, const float* bias, int act,
                                float* out, cudaStream_t s)
 {
-    if (!pf_tile_covers(p)) return -1;
+    if (!e->cols_ascending || !pf_tile_covers(p)) return -1;
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
     // batch entries per CTA: the largest multiple of 4 that divides B and is <= 32
     uint32_t BT = 0;
     for (uint32_t c = 32; c >= 4; c -= 4) if (p.B % c == 0) { BT = c; break; }
     if (!BT) return -1;
+    {
+        const int rc = launch_conv_rbm_tile(e, p, BT, in, bias, act, out, s);
+        if (rc != -1) return rc;
+    }
     static const int ctas = [] { const char* v = getenv("SPX_CONV_CTAS"); return v ? atoi(v) : 0; }();
     static const int small_tile = [] { const char* v = getenv("SPX_CONV_SMALL_TILE"); return v ? atoi(v) : -1; }();
     // Full batch tile (32 entries): 2 x 8 positions per warp and 32 warps (= output channels) per
@@ -390,7 +692,7 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
         int rc2 = launch_conv_pf_tile(e, p, in, bias, act, out, s);
         if (rc2 != -1) return rc2;           // -1: shape not covered by the tiled kernel
     }
-    if (layout == SPX_LAYOUT_NCHW && e->r && B > 1 && pf_tile_covers(p)) {
+    if (layout == SPX_LAYOUT_NCHW && e->r && B > 1 && e->cols_ascending && pf_tile_covers(p)) {
         // NCHW: transpose to [C,H,W,B] in per-handle scratch, run the tiled kernel, transpose back.
         // Two extra streaming passes over input and output (about 7 % of the kernel's time at
         // 256 channels) instead of a second gather kernel; arithmetic per element is unchanged.

@@ -142,7 +142,7 @@ def cfg3(scale: float = 1.0, seed: int = 44, batch: int | None = None):
 
 
 # ---- config 4: sparse 3x3 conv 256->256 on 56x56, batch 32, 80 % sparse ------------------------
-def cfg4(scale: float = 1.0, seed: int = 45, layers: int = 1):
+def cfg4(scale: float = 1.0, seed: int = 45, layers: int = 1, density: float = 0.2):
     Cc = max(4, int(256 * scale))
     H = W = max(6, int(56 * scale))
     B = max(2, int(32 * scale))
@@ -150,7 +150,7 @@ def cfg4(scale: float = 1.0, seed: int = 45, layers: int = 1):
     for l in range(layers):
         g = _rng(seed, 10 + l)
         w = g.standard_normal((Cc, Cc, 3, 3), dtype=np.float32) * np.float32(np.sqrt(2.0 / (9 * Cc)))
-        w[g.random((Cc, Cc, 3, 3), dtype=np.float32) >= 0.2] = 0.0
+        w[g.random((Cc, Cc, 3, 3), dtype=np.float32) >= np.float32(density)] = 0.0
         ws.append(w)
         bs.append(_rng(seed, 20 + l).standard_normal(Cc).astype(np.float32))
     x = _rng(seed, 1).standard_normal((B, Cc, H, W), dtype=np.float32)

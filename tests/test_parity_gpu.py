@@ -5,6 +5,8 @@ Bars: ELLPACK encodings, SpMM and conv outputs bit-exact (a thread owns whole ou
 runs the reference's FMA chain in storage order); SpMV within 1e-5 * (sum_j |w||x| + |bias|) per
 element (the summation order differs from the reference's 16 partial sums); sigmoid / tanh
 epilogues within 4 ulp-ish relative 1e-6 of the C library."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -237,6 +239,49 @@ def test_conv_bit_exact_vs_oracle(lib, orc, cuda, layout, B, Cin, Cout, H, W, k,
     got = dY.cpu().numpy()
     got_nchw = got.transpose(3, 0, 1, 2) if layout == sx.LAYOUT_PF else got
     assert np.abs(got_nchw - ref).max() <= 1e-4
+
+
+@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW])
+def test_conv_unsorted_columns(lib, orc, cuda, layout):
+    """Raw ELLPACK arrays may store a row's columns in any order (spx_ell_create only checks the range).
+    The tiled kernels need ascending columns; such a handle must take the general kernel and still
+    apply the FMAs in storage order, like the CPU restatement does."""
+    B, Cin, Cout, H, W, k = 16, 16, 12, 10, 10, 3
+    rng = np.random.default_rng(77)
+    wt = sparse(rng, Cout, Cin * k * k, 0.3) * np.float32(0.3)
+    E = orc.encode(wt)
+    for i in range(E.m):                                  # shuffle every row's stored entries
+        c = int(E.nnz[i])
+        perm = rng.permutation(c)
+        E.Wd[i, :c] = E.Wd[i, :c][perm]
+        E.idx[i, :c] = E.idx[i, :c][perm]
+    bias = rng.standard_normal(Cout).astype(np.float32)
+    x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
+    src = np.ascontiguousarray(x.transpose(1, 2, 3, 0)) if layout == sx.LAYOUT_PF else x
+    gd = dict(Cin=Cin, kH=k, kW=k, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+    want = orc.conv2d(E, gd, layout, src, B, bias, 1)
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(Cin, Cout, k, k, H, W, 1, 1, 1, 1, 1, 1)
+    dX, dB = dev(src, cuda), dev(bias, cuda)
+    dY = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
+    h.conv2d(g, layout, ptr(dX), B, ptr(dB), sx.ACT_RELU, ptr(dY))
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), want, "conv, unsorted columns")
+
+
+@pytest.mark.parametrize("env", [{"SPX_CONV_RBM": "0"}, {"SPX_CONV_RBM_MIN_SHARE": "0"}, {"SPX_CONV_DIRECT": "1"}],
+                         ids=["per-row-tiles", "row-block-merged", "direct"])
+def test_conv_each_kernel_forced(env):
+    """The library picks a convolution kernel from batch size and density; the switches are read
+    once per process, so each kernel is forced in a child process that reruns the conv parity cases."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+           os.path.join(here, "test_parity_gpu.py"), os.path.join(here, "test_fuzz_gpu.py"),
+           "-k", "conv_bit_exact or conv_random or golden_conv"]
+    r = subprocess.run(cmd, env={**os.environ, **env}, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
 
 def test_conv_rejects_bad_geometry(lib, orc, cuda):
