@@ -1,4 +1,4 @@
-"""Minimal ONNX protobuf wire-format WRITER (no `onnx` / protobuf package needed).
+"""Minimal ONNX protobuf wire-format writer and reader (no `onnx` / protobuf package needed).
 
 Produces the small subset of ONNX graphs that `SparseOnnxModel` loads: Gemm / MatMul / Conv /
 Relu / Sigmoid / Tanh / Identity nodes, float32 initialisers, one static-shape input and
@@ -128,3 +128,114 @@ def conv_model(weights, biases, relus, batch: int, H: int, W: int, stride=1, pad
     cin = weights[0].shape[1]
     cout = weights[-1].shape[0]
     return model(nodes, inits, ("input", (batch, cin, H, W)), (cur, (batch, cout, h, w)))
+
+
+# ---- reader (the subset the pure-Python runtime sparse_onnx.OnnxSparseModel needs) --------------
+def _fields(buf: bytes):
+    """Yields (field number, wire type, value) of one message; value is an int (varint, fixed) or bytes."""
+    i, n = 0, len(buf)
+    while i < n:
+        key = shift = 0
+        while True:
+            b = buf[i]; i += 1
+            key |= (b & 0x7F) << shift
+            shift += 7
+            if not b & 0x80:
+                break
+        field, wt = key >> 3, key & 7
+        if wt == 0:
+            v = shift = 0
+            while True:
+                b = buf[i]; i += 1
+                v |= (b & 0x7F) << shift
+                shift += 7
+                if not b & 0x80:
+                    break
+            yield field, wt, v
+        elif wt == 1:
+            yield field, wt, int.from_bytes(buf[i:i + 8], "little"); i += 8
+        elif wt == 5:
+            yield field, wt, int.from_bytes(buf[i:i + 4], "little"); i += 4
+        elif wt == 2:
+            ln = shift = 0
+            while True:
+                b = buf[i]; i += 1
+                ln |= (b & 0x7F) << shift
+                shift += 7
+                if not b & 0x80:
+                    break
+            if i + ln > n:
+                raise ValueError("truncated ONNX file")
+            yield field, wt, bytes(buf[i:i + ln]); i += ln
+        else:
+            raise ValueError(f"unsupported protobuf wire type {wt}")
+
+
+def _varints(payload: bytes):
+    out, v, shift = [], 0, 0
+    for b in payload:
+        v |= (b & 0x7F) << shift
+        shift += 7
+        if not b & 0x80:
+            out.append(v); v = shift = 0
+    return out
+
+
+def _read_tensor(buf: bytes):
+    dims, dtype, name, raw, floats = [], 1, "", None, []
+    for f, wt, v in _fields(buf):
+        if f == 1:
+            dims += _varints(v) if wt == 2 else [v]
+        elif f == 2:
+            dtype = v
+        elif f == 4:                                   # float_data, packed or one fixed32 each
+            floats.append(v if wt == 2 else int(v).to_bytes(4, "little"))
+        elif f == 8:
+            name = v.decode()
+        elif f == 9:
+            raw = v
+    if dtype != 1:
+        return name, None                              # only float32 initialisers carry weights here
+    data = raw if raw is not None else b"".join(floats)
+    return name, np.frombuffer(data, dtype="<f4").reshape(dims).copy()
+
+
+def _read_node(buf: bytes):
+    nd = dict(op_type="", input=[], output=[], attrs={})
+    for f, wt, v in _fields(buf):
+        if f == 1:
+            nd["input"].append(v.decode())
+        elif f == 2:
+            nd["output"].append(v.decode())
+        elif f == 4:
+            nd["op_type"] = v.decode()
+        elif f == 5:
+            name, val, ints = "", None, []
+            for af, awt, av in _fields(v):
+                if af == 1:
+                    name = av.decode()
+                elif af == 3:
+                    val = av - (1 << 64) if av >> 63 else av
+                elif af == 8:
+                    ints += _varints(av) if awt == 2 else [av]
+            nd["attrs"][name] = ints if ints else val
+    return nd
+
+
+def read_model(data: bytes):
+    """Parses ModelProto bytes into {'nodes': [...], 'initializers': {name: float32 array}}."""
+    graph = None
+    for f, wt, v in _fields(data):
+        if f == 7 and wt == 2:
+            graph = v
+    if graph is None:
+        raise ValueError("no graph in ONNX file")
+    nodes, inits = [], {}
+    for f, wt, v in _fields(graph):
+        if f == 1 and wt == 2:
+            nodes.append(_read_node(v))
+        elif f == 5 and wt == 2:
+            name, arr = _read_tensor(v)
+            if arr is not None:
+                inits[name] = arr
+    return dict(nodes=nodes, initializers=inits)

@@ -192,3 +192,25 @@ def test_planner_cnn_with_pools_and_flatten(backend):
     finally:
         os.unlink(path)
     assert [l["op"] for l in m.layer_summary()] == ["GlobalAveragePool"] and m.output_shape() == [2, 3]
+
+
+def test_python_onnx_reader_round_trip():
+    """The pure-Python reader behind sparse_onnx.OnnxSparseModel parses what the writer emits:
+    nodes, attributes, raw_data and packed float_data initialisers."""
+    import onnx_wire as ow
+    rng = np.random.default_rng(5)
+    Ws = [rng.standard_normal((6, 5)).astype(np.float32), rng.standard_normal((3, 6)).astype(np.float32)]
+    bs = [rng.standard_normal(6).astype(np.float32), rng.standard_normal(3).astype(np.float32)]
+    m = ow.read_model(ow.mlp_model(Ws, bs, ["Relu", "Sigmoid"], 4))
+    assert [n["op_type"] for n in m["nodes"]] == ["Gemm", "Relu", "Gemm", "Sigmoid"]
+    assert m["nodes"][0]["input"] == ["input", "W0", "b0"] and m["nodes"][0]["attrs"] == {"transB": 1}
+    for l in range(2):
+        assert np.array_equal(m["initializers"][f"W{l}"], Ws[l]) and np.array_equal(m["initializers"][f"b{l}"], bs[l])
+    packed = ow.model([ow.node("MatMul", ["input", "W"], ["out"])], [ow.tensor("W", Ws[0].T, packed_float_data=True)],
+                      ("input", (4, 6)), ("out", (4, 5)))
+    assert np.array_equal(ow.read_model(packed)["initializers"]["W"], Ws[0].T)
+    conv = ow.read_model(ow.conv_model([rng.standard_normal((4, 3, 3, 3)).astype(np.float32)], [np.zeros(4, np.float32)],
+                                       [True], 2, 8, 8, stride=2, pad=1, dil=1))
+    assert conv["nodes"][0]["attrs"]["strides"] == [2, 2] and conv["nodes"][0]["attrs"]["pads"] == [1, 1, 1, 1]
+    with pytest.raises(ValueError):
+        ow.read_model(ow.mlp_model(Ws, bs, ["Relu", None], 4)[:-7])      # truncated file

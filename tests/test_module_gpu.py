@@ -269,3 +269,37 @@ def test_model_conv_stack_config4_scaled_vs_oracle(backend, orc, cuda):
     for wgt, b in zip(d["weights"], d["biases"]):
         a = orc.conv2d(orc.encode(wgt.reshape(Cc, -1)), g, 0, a, B, b, 1)
     assert_bit_equal(y, a, "conv stack")
+
+
+def test_python_onnx_sparse_model(backend, cuda):
+    """OnnxSparseModel (the pure-Python loop of the reference's python/sparse_onnx.py) over these
+    bindings: weights are encoded as stored, a 1-D input takes matvec, a 2-D (n, C) input matmul."""
+    import onnx_wire as ow
+    from sparse_onnx import OnnxSparseModel
+    rng = np.random.default_rng(31)
+    dims = [40, 64, 48, 10]
+    Ws = [generate_sparse_matrix(dims[l + 1], dims[l], 0.6, seed=l) - 0.5 * (generate_sparse_matrix(dims[l + 1], dims[l], 0.6, seed=l) != 0)
+          for l in range(3)]
+    bs = [rng.standard_normal(dims[l + 1]).astype(np.float32) for l in range(3)]
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "mlp.onnx")
+        with open(path, "wb") as f:
+            f.write(ow.mlp_model(Ws, bs, ["Relu", "Tanh", "Sigmoid"], 8))
+        model = OnnxSparseModel(path)
+        bad = os.path.join(d, "conv.onnx")
+        with open(bad, "wb") as f:
+            f.write(ow.conv_model([rng.standard_normal((4, 3, 3, 3)).astype(np.float32)], [np.zeros(4, np.float32)], [True], 2, 8, 8))
+        with pytest.raises(NotImplementedError):
+            OnnxSparseModel(bad)
+    assert [l[0] for l in model.layers] == ["matmul", "relu", "matmul", "tanh", "matmul", "sigmoid"]
+
+    def dense(v):
+        v = np.maximum(Ws[0].astype(np.float64) @ v + bs[0][(...,) + (None,) * (v.ndim - 1)], 0)
+        v = np.tanh(Ws[1].astype(np.float64) @ v + bs[1][(...,) + (None,) * (v.ndim - 1)])
+        return 1 / (1 + np.exp(-(Ws[2].astype(np.float64) @ v + bs[2][(...,) + (None,) * (v.ndim - 1)])))
+
+    x1 = rng.standard_normal(40).astype(np.float32)
+    X = rng.standard_normal((40, 8)).astype(np.float32)
+    y1, Y = model.run(x1), model.run(X)
+    assert y1.shape == (10,) and Y.shape == (10, 8) and Y.dtype == np.float32
+    assert np.abs(y1 - dense(x1)).max() <= 1e-5 and np.abs(Y - dense(X)).max() <= 1e-5
