@@ -139,15 +139,19 @@ int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void
 int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias, float* y, void* stream);
 /* Sparse convolution by implicit im2col; e is the ELLPACK of the weight flattened to
  * [Cout x Cin*kH*kW].  Replaces conv2d_patchmajor_tiled / conv2d_tiled_im2col_cmajor /
- * conv2d_tiled_im2col_fmajor / conv2d_rbm_fmajor_implicit (src/layers/conv_kernels.cpp:66-470). */
+ * conv2d_tiled_im2col_fmajor / conv2d_rbm_fmajor_implicit (src/layers/conv_kernels.cpp:66-470)
+ * and, on the device, build_rbm_from_ellpack (src/layers/rbm_conv.cpp:7-73): the first call per
+ * handle and kernel shape builds and caches a tap table and, where the batch size and weight
+ * density favour it, the row-block-merged form of the weights (device allocations; make that
+ * call outside a stream capture).  Results do not depend on which kernel is chosen. */
 int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                const float* bias, int act, float* out, void* stream);
 /* spx_conv2d for callers that must not allocate device memory (no counterpart in the
  * reference, which runs on the CPU).  Some hosts hand all device memory to their own pool at
  * start-up, so a later cudaMalloc has nothing to take, and a latency-bound serving loop cannot
- * accept the device-wide synchronisation an allocation may imply.  spx_conv2d allocates a tap
- * table per handle on first use; this variant keeps that table in a fixed 4 MiB array inside the
- * library image instead (held by every GPU that loads the library until the process exits) and
+ * accept the device-wide synchronisation an allocation may imply.  spx_conv2d allocates its
+ * per-handle tables on first use; this variant keeps the one table it needs in a fixed 4 MiB
+ * array inside the library image instead (held by every GPU that loads the library until the process exits) and
  * calls no cudaMalloc / cudaFree or allocating routine.  Limits and rules: Cout * (r rounded up
  * to 32) must not exceed 1 048 576 slots, else SPX_ERR_LIMIT; the handle's device must be
  * current; all calls share the one array, so calls that overlap on the GPU race -- serialise
