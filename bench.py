@@ -26,6 +26,7 @@ on a bounded sample of the same workload.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -748,6 +749,27 @@ def measure(args, c):
         fused = {"ms_per_step": f_sec * 1e3, "value": to_value(wk, job_bytes, f_sec),
                  "note": "SpMM whose epilogue stores Y into every rank's full buffer over NVLink (peer stores) + barrier"}
 
+    # Measured denominator for the SpMM operand path: random 512-byte gathers from an L2-resident
+    # buffer, L1 bypassed (spx_probe_l2_gather), timed here on this GPU right after the workload.
+    l2_gather_tbps = None
+    if rank == 0 and kind in ("spmm", "mlp"):
+        probe_buf = torch.empty(32 << 20, dtype=torch.uint8, device=dev)
+        probe_buf.zero_()
+        sink = torch.zeros(1, dtype=torch.float32, device=dev)
+        nbytes = ctypes.c_uint64(0)
+        stream_ptr = torch.cuda.current_stream().cuda_stream
+        best = 0.0
+        for i in range(5):                              # first pass warms L2; best of the rest
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            lib.spx_probe_l2_gather(probe_buf.data_ptr(), 32 << 20, 200, sink.data_ptr(), stream_ptr, ctypes.byref(nbytes))
+            e1.record()
+            torch.cuda.synchronize()
+            if i:
+                best = max(best, nbytes.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        l2_gather_tbps = best
+        del probe_buf
+
     if rank == 0:
         metric, unit = metric_of(wk, args)
         peak, peak_kind = measured_peak()
@@ -781,6 +803,12 @@ def measure(args, c):
                         "shared memory, once per FMA by the per-row kernel, once per block of 4 rows by the "
                         "row-block-merged kernel)",
                 "bytes_per_step": op_bytes, "achieved_tbps": op_bytes / sec / 1e12}
+            if l2_gather_tbps:
+                line["roofline"]["operand_path"].update({
+                    "l2_gather_peak_tbps": l2_gather_tbps,
+                    "frac_of_l2_gather_peak": op_bytes / sec / 1e12 / l2_gather_tbps,
+                    "peak_source": "spx_probe_l2_gather on this GPU: random 512-byte gathers from a 32 MiB buffer, "
+                                   "L1 bypassed; operands served by L1 hits can lift the fraction above 1"})
         if e2e:
             line["e2e"] = e2e
         if ag:

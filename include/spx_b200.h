@@ -95,6 +95,14 @@ int spx_event_destroy(void* event);
 int spx_event_record(void* event, void* stream);
 int spx_event_elapsed_ms(void* start, void* stop, float* ms);   /* synchronises on stop */
 
+/* Measurement aid, no counterpart in the reference: gathers 512-byte segments at pseudo-random
+ * positions of buf (first power-of-two number of segments within `bytes`; choose a size that
+ * fits L2), bypassing L1, `rounds` x 8 loads per lane on a full grid, and reports how many
+ * bytes the launch reads.  bytes_read / device time = the L2 -> SM gather bandwidth that the
+ * SpMM's operand traffic is compared with (bench.py).  sink: one writable float on the device. */
+int spx_probe_l2_gather(const void* buf, size_t bytes, uint32_t rounds, float* sink, void* stream,
+                        uint64_t* bytes_read);
+
 /* ---- CUDA graphs (the captured layer loop of SparseOnnxModel::run) ---------------------- */
 int spx_graph_capture_begin(void* stream);
 int spx_graph_capture_end(void* stream, void** graph_exec);

@@ -9,4 +9,4 @@ exec $NVCC -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -fma
     -Xcompiler -fPIC -shared -I../include -Icsrc/cuda \
     ${SPX_PTXAS_V:+-Xptxas -v} \
     -o libspx_b200.so csrc/cuda/abi.cu csrc/cuda/comm.cu csrc/cuda/spmm.cu csrc/cuda/spmv.cu \
-    csrc/cuda/conv.cu csrc/cuda/pool.cu csrc/cuda/eltwise.cu csrc/cuda/encode.cu -ldl
+    csrc/cuda/conv.cu csrc/cuda/pool.cu csrc/cuda/eltwise.cu csrc/cuda/encode.cu csrc/cuda/probe.cu -ldl

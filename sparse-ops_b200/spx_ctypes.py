@@ -61,6 +61,7 @@ SIGNATURES = {
     "spx_memcpy_d2h": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "spx_memcpy_d2d": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "spx_memset": (C.c_int, [_vp, C.c_int, C.c_size_t, _vp]),
+    "spx_probe_l2_gather": (C.c_int, [_vp, C.c_size_t, C.c_uint32, _vp, _vp, C.POINTER(C.c_uint64)]),
     "spx_stream_create": (C.c_int, [C.POINTER(_vp)]),
     "spx_stream_destroy": (C.c_int, [_vp]),
     "spx_stream_sync": (C.c_int, [_vp]),

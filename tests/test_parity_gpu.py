@@ -528,3 +528,17 @@ def test_abi_rejects_misuse_with_status_codes(lib, orc, cuda):
     h.spmv(x.data_ptr(), 0, y.data_ptr())              # still works
     torch.cuda.synchronize()
     assert y.cpu().numpy().tolist() == [1.0] * 8
+
+
+def test_l2_gather_probe_runs(lib, cuda):
+    """The measurement aid reads what it reports and leaves the sink alone."""
+    import ctypes
+    buf = torch.zeros(8 << 20, dtype=torch.uint8, device=cuda)
+    sink = torch.full((1,), 7.0, dtype=torch.float32, device=cuda)
+    n = ctypes.c_uint64(0)
+    lib.spx_probe_l2_gather(buf.data_ptr(), 8 << 20, 4, sink.data_ptr(), 0, ctypes.byref(n))
+    torch.cuda.synchronize()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert n.value == sms * 8 * 8 * 4 * 8 * 512 and float(sink.item()) == 7.0
+    with pytest.raises(sx.SpxError):
+        lib.spx_probe_l2_gather(buf.data_ptr(), 512, 4, sink.data_ptr(), 0, ctypes.byref(n))
