@@ -15,7 +15,9 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <climits>
 #include <cmath>
+#include <cstdint>
 #include <cstdlib>
 
 namespace {
@@ -539,10 +541,19 @@ static int ensure_rbm(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
     if (e->rbm_hdr && e->rbm_kH == kH && e->rbm_kW == kW) return SPX_OK;
     const uint32_t nblocks = (e->m + kRbmRows - 1) / kRbmRows;
     if (!e->rbm_hdr) {
+        // Up to three times the ELLPACK slab (24 bytes per union column, at most 4 * max_nnz columns
+        // per block of 4 rows).  Without room for it the per-row kernel is used instead.
+        if (e->rbm_cap == UINT32_MAX) return -1;        // an earlier attempt ran out of memory
         const uint32_t cap = (uint32_t)std::min<uint64_t>((uint64_t)kRbmRows * e->max_nnz, e->n);
-        SPX_CUDA(cudaMalloc(&e->rbm_ncols, (size_t)nblocks * sizeof(uint32_t)));
-        SPX_CUDA(cudaMalloc(&e->rbm_w, (size_t)nblocks * cap * kRbmRows * sizeof(float)));
-        SPX_CUDA(cudaMalloc(&e->rbm_hdr, (size_t)nblocks * cap * sizeof(uint2)));
+        if (cudaMalloc(&e->rbm_ncols, (size_t)nblocks * sizeof(uint32_t)) != cudaSuccess ||
+            cudaMalloc(&e->rbm_w, (size_t)nblocks * cap * kRbmRows * sizeof(float)) != cudaSuccess ||
+            cudaMalloc(&e->rbm_hdr, (size_t)nblocks * cap * sizeof(uint2)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cudaFree(e->rbm_ncols); cudaFree(e->rbm_w); cudaFree(e->rbm_hdr);
+            e->rbm_ncols = nullptr; e->rbm_w = nullptr; e->rbm_hdr = nullptr;
+            e->rbm_cap = UINT32_MAX;
+            return -1;
+        }
         e->rbm_cap = cap;
     }
     const size_t smem = (size_t)((e->n + 31) / 32) * 2 * sizeof(uint32_t);
@@ -574,7 +585,7 @@ static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float
     const uint32_t gy = (nblocks + NB - 1) / NB, gz = p.B / tp.BT;
     if (tiles > 0x7fffffffull || gy > 65535 || gz > 65535) return -1;
     const int rc = ensure_rbm(e, p.kH, p.kW, s);
-    if (rc != SPX_OK) return rc;
+    if (rc != SPX_OK) return rc;                        // -1: no memory for the merged weights
     const size_t smem = chanBytes * tp.CC;
     auto kfn = conv_rbm_tile_kernel<QB, NB>;
     cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
