@@ -138,7 +138,9 @@ int spx_ell_decode_device(const spx_ell* e, float* dW, void* stream);
 int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
              int act, float* Y, uint64_t ldy, void* stream);
 /* y[i] = bias[i] + sum_j Wd[i,j] * x[idx[i,j]].  Replaces ellpack_matvec
- * (src/ellpack_matvec.cpp:20-147).  bias may be NULL. */
+ * (src/ellpack_matvec.cpp:20-147).  bias may be NULL.  For n above 51200 (x larger than shared
+ * memory) the first call builds and caches a per-row table of column-window boundaries in the
+ * handle (a device allocation of up to 28 bytes per row; make that call outside a stream capture). */
 int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void* stream);
 /* spx_spmv in the reference's own summation order (sixteen partial sums by j mod 16, then the
  * pairwise tree of src/ellpack_matvec.cpp:88-96): bit-identical to the reference's AVX-512 path,

@@ -377,7 +377,7 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
-    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
     for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
     delete e;
     return SPX_OK;
@@ -469,7 +469,7 @@ int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void
     if (e->m == 0) return SPX_OK;
     if (!y) return fail(SPX_ERR_ARG, "y is null");
     if (!x && e->nnz_total) return fail(SPX_ERR_ARG, "x is null");
-    return launch_spmv(e, x, bias, y, (cudaStream_t)stream);
+    return launch_spmv(const_cast<spx_ell*>(e), x, bias, y, (cudaStream_t)stream);
 }
 
 int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias, float* y, void* stream)

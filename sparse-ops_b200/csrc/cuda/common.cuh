@@ -43,6 +43,10 @@ struct spx_ell {
     float* rbm_w = nullptr;
     uint32_t* rbm_ncols = nullptr;
     uint32_t rbm_cap = 0, rbm_kH = 0, rbm_kW = 0;
+    // SpMV with x larger than shared memory (spmv.cu): column window width and the per-row split
+    // table, built on the first spx_spmv of such a handle.  spmv_win == UINT32_MAX: not applicable.
+    uint32_t* spmv_split = nullptr;
+    uint32_t spmv_win = 0;
     // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
     void* stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
@@ -100,7 +104,7 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
                 int act, float* Y, uint64_t ldy, cudaStream_t s);
 int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
                       float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s);
-int launch_spmv(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
+int launch_spmv(spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
 int launch_spmv_reforder(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                   const float* bias, int act, float* out, cudaStream_t s);

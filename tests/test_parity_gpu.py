@@ -133,7 +133,7 @@ def test_spmm_sigmoid_tanh_epilogue(lib, orc, cuda, act):
 SPMV_CASES = [(16, 32, 0.7), (64, 128, 0.5), (128, 256, 0.3), (256, 512, 0.1), (1, 1, 1.0), (1, 1000, 0.9),
               (1000, 1, 0.9), (32, 32, 0.0), (10, 10, 1.0), (10, 10, 0.5), (20, 20, 0.8), (100, 100, 0.8),
               (1000, 1000, 0.9), (500, 500, 0.95), (2000, 2000, 0.7), (3000, 3000, 0.6), (4096, 4096, 0.01),
-              (300, 20000, 0.05), (70, 70000, 0.02), (50, 210000, 0.01)]
+              (300, 20000, 0.05), (70, 70000, 0.02), (50, 210000, 0.01), (20, 450000, 0.002)]
 
 
 @pytest.mark.parametrize("m,n,p", SPMV_CASES)
