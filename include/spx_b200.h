@@ -11,7 +11,8 @@
  *     entry points only enqueue work; they do not synchronise.
  *   - A handle may be used from several host threads for kernel launches, but entry points
  *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, the NCHW layout,
- *     the *_host calls) must not run concurrently on the same handle.
+ *     the first spx_spmv of a handle with n > 51200, the *_host calls) must not run concurrently
+ *     on the same handle.
  *   - There is no CPU fallback: without a usable CUDA device every compute entry point
  *     fails with SPX_ERR_CUDA.
  *
