@@ -369,14 +369,14 @@ constexpr int kRbmG = 4;                                 // float4 groups per la
 
 // One row of the block: when the union column holds an entry of row R, fetch its weight from the
 // lane that preloaded the column and run the row's 16 FMAs.  The test is warp-uniform.
-template <int R>
-__device__ __forceinline__ void rbm_row(float4 (&acc)[kRbmRows][kRbmG], uint32_t hm, float wsrc, uint32_t t,
-                                        const float4 (&x)[kRbmG])
+template <int R, int G>
+__device__ __forceinline__ void rbm_row(float4 (&acc)[kRbmRows][G], uint32_t hm, float wsrc, uint32_t t,
+                                        const float4 (&x)[G])
 {
     if (hm & (1u << R)) {
         const float wt = __shfl_sync(0xffffffffu, wsrc, t);
 #pragma unroll
-        for (int g = 0; g < kRbmG; ++g) {
+        for (int g = 0; g < G; ++g) {
             acc[R][g].x = fmaf(wt, x[g].x, acc[R][g].x);
             acc[R][g].y = fmaf(wt, x[g].y, acc[R][g].y);
             acc[R][g].z = fmaf(wt, x[g].z, acc[R][g].z);
@@ -385,23 +385,35 @@ __device__ __forceinline__ void rbm_row(float4 (&acc)[kRbmRows][kRbmG], uint32_t
     }
 }
 
-template <int QB, int NB>
+// Work units are (tile of positions, group of NB row blocks, batch tile), numbered tile-fastest.
+// G = kRbmG: the CTA takes unit `unit0 + blockIdx.x`.  G = kRbmG / 2 (half-height tiles): CTAs
+// 2u and 2u + 1 take the upper and lower half of unit `unit0 + u`; used for the last, partly
+// filled wave of a launch so that its work spreads over twice as many SMs.
+struct RbmUnits {
+    uint32_t unit0, tiles, groups;     // first unit of this launch; tiles per image; row-block groups
+};
+
+template <int QB, int NB, int G>
 __global__ void __launch_bounds__(NB * 32, 1)
 conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w4,
-                     const uint32_t* __restrict__ ncols, uint32_t cap, TileParams tp,
+                     const uint32_t* __restrict__ ncols, uint32_t cap, TileParams tp, RbmUnits un,
                      const float* __restrict__ in, const float* __restrict__ bias, int act,
                      float* __restrict__ out)
 {
     extern __shared__ __align__(16) float tile[];
-    constexpr int G = kRbmG, RB = (int)kRbmRows;
+    constexpr int RB = (int)kRbmRows;
     constexpr uint32_t BT = QB * 4;
     constexpr uint32_t TH = 32u * G / QB / kTileW;       // rows of output positions per tile
+    constexpr bool kHalf = G != kRbmG;
     const ConvParams& p = tp.c;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t ty = blockIdx.x / tp.tilesX, tx = blockIdx.x % tp.tilesX;
+    const uint32_t unit = un.unit0 + (kHalf ? blockIdx.x >> 1 : blockIdx.x);
+    const uint32_t t_id = unit % un.tiles, by = (unit / un.tiles) % un.groups, bz = unit / un.tiles / un.groups;
+    const uint32_t ty = kHalf ? (t_id / tp.tilesX) * 2 + (blockIdx.x & 1) : t_id / tp.tilesX, tx = t_id % tp.tilesX;
     const uint32_t oh0 = ty * TH, ow0 = tx * kTileW;
-    const uint32_t b0 = blockIdx.z * BT;
-    const uint32_t blk = blockIdx.y * NB + warp;
+    if (oh0 >= p.Ho) return;                             // lower half of a tile that ends above it
+    const uint32_t b0 = bz * BT;
+    const uint32_t blk = by * NB + warp;
     const uint32_t mo0 = blk * RB;
     const bool active = mo0 < p.Cout;
     const int ih0 = (int)(oh0 * p.sH) - (int)p.pH;
@@ -448,10 +460,10 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
                     float4 x[G];
 #pragma unroll
                     for (int g = 0; g < G; ++g) x[g] = *reinterpret_cast<const float4*>(xs + off[g]);
-                    rbm_row<0>(acc, hm, wl.x, t, x);
-                    rbm_row<1>(acc, hm, wl.y, t, x);
-                    rbm_row<2>(acc, hm, wl.z, t, x);
-                    rbm_row<3>(acc, hm, wl.w, t, x);
+                    rbm_row<0, G>(acc, hm, wl.x, t, x);
+                    rbm_row<1, G>(acc, hm, wl.y, t, x);
+                    rbm_row<2, G>(acc, hm, wl.z, t, x);
+                    rbm_row<3, G>(acc, hm, wl.w, t, x);
                 }
                 pos += cnt;
                 if (cnt < 32) break;
@@ -565,6 +577,29 @@ static int ensure_rbm(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
     return SPX_OK;
 }
 
+template <int QB, int G>
+static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32_t ctas, const float* in, const float* bias,
+                            int act, float* out, cudaStream_t s)
+{
+    constexpr int NB = 16;
+    const ConvParams& p = tp.c;
+    constexpr uint32_t TH = 32u * G / QB / kTileW;
+    tp.BT = QB * 4;
+    tp.THin = (TH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
+    tp.TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
+    const size_t chanBytes = (size_t)tp.THin * tp.TWin * tp.BT * sizeof(float);
+    const size_t budget = 200 * 1024;
+    tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
+    const size_t smem = chanBytes * tp.CC;
+    auto kfn = conv_rbm_tile_kernel<QB, NB, G>;
+    cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    kfn<<<ctas, NB * 32, smem, s>>>(e->rbm_hdr, reinterpret_cast<const float4*>(e->rbm_w), e->rbm_ncols, e->rbm_cap,
+                                    tp, un, in, bias, act, out);
+    SPX_LAUNCH_CHECK("conv_rbm_tile_kernel");
+    return SPX_OK;
+}
+
 template <int QB>
 static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float* bias, int act, float* out,
                          cudaStream_t s)
@@ -572,35 +607,38 @@ static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float
     constexpr int NB = 16;
     const ConvParams& p = tp.c;
     constexpr uint32_t TH = 32u * kRbmG / QB / kTileW;
-    tp.BT = QB * 4;
-    tp.THin = (TH - 1) * p.sH + (p.kH - 1) * p.dH + 1;
-    tp.TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
-    const size_t chanBytes = (size_t)tp.THin * tp.TWin * tp.BT * sizeof(float);
-    const size_t budget = 200 * 1024;
-    if (chanBytes > budget) return -1;
-    tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
+    const uint32_t THin = (TH - 1) * p.sH + (p.kH - 1) * p.dH + 1, TWin = (kTileW - 1) * p.sW + (p.kW - 1) * p.dW + 1;
+    if ((size_t)THin * TWin * QB * 4 * sizeof(float) > 200 * 1024) return -1;
     tp.tilesX = (p.Wo + kTileW - 1) / kTileW;
     const uint64_t tiles = (uint64_t)tp.tilesX * ((p.Ho + TH - 1) / TH);
     const uint32_t nblocks = (p.Cout + kRbmRows - 1) / kRbmRows;
-    const uint32_t gy = (nblocks + NB - 1) / NB, gz = p.B / tp.BT;
-    if (tiles > 0x7fffffffull || gy > 65535 || gz > 65535) return -1;
+    const uint32_t groups = (nblocks + NB - 1) / NB;
+    const uint64_t units = tiles * groups * (p.B / (QB * 4));
+    if (units > 0x3fffffffull) return -1;
     const int rc = ensure_rbm(e, p.kH, p.kW, s);
     if (rc != SPX_OK) return rc;                        // -1: no memory for the merged weights
-    const size_t smem = chanBytes * tp.CC;
-    auto kfn = conv_rbm_tile_kernel<QB, NB>;
-    cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
-    kfn<<<dim3((unsigned)tiles, gy, gz), NB * 32, smem, s>>>(e->rbm_hdr, reinterpret_cast<const float4*>(e->rbm_w),
-                                                           e->rbm_ncols, e->rbm_cap, tp, in, bias, act, out);
-    SPX_LAUNCH_CHECK("conv_rbm_tile_kernel");
-    return SPX_OK;
+    // One CTA per SM, all units equally long: the launch runs in waves of sm_count units.  A last
+    // wave that fills less than half of the SMs is issued as a second launch of half-height tiles
+    // (twice the CTAs, each about 0.6 of a full unit's time): 784 units on 148 SMs are 5 full waves
+    // + 44 units -> 5 waves + 88 half units.  SPX_CONV_RBM_SPLIT_TAIL=0 keeps one launch.
+    static const int split_tail = [] { const char* v = getenv("SPX_CONV_RBM_SPLIT_TAIL"); return v ? atoi(v) : 1; }();
+    const uint32_t sms = (uint32_t)sm_count(e->device);
+    const uint32_t rem = (uint32_t)(units % sms);
+    RbmUnits un{0u, (uint32_t)tiles, groups};
+    if (split_tail && units > sms && rem && rem * 2 <= sms) {
+        const int rc1 = launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)(units - rem), in, bias, act, out, s);
+        if (rc1 != SPX_OK) return rc1;
+        un.unit0 = (uint32_t)(units - rem);
+        return launch_rbm_units<QB, kRbmG / 2>(e, tp, un, rem * 2, in, bias, act, out, s);
+    }
+    return launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)units, in, bias, act, out, s);
 }
 
 // Row-block-merged path.  Taken when K fits the builder's set and the expected number of rows per
 // union column, 4 d / (1 - (1 - d)^4) for density d, pays for the mask tests.  Measured against
 // conv_pf_tile_kernel on 256 -> 256 channels, 3 x 3, 56 x 56:
 //   batch a multiple of 16: tiles of 16 entries (faster than 32: twice the channels per staged
-//     chunk); wins from 80 % sparsity down (1.83 vs 1.89 ms at 80 %, 2.93 vs 4.15 ms at 50 %,
+//     chunk); wins from 80 % sparsity down (1.69 vs 1.89 ms at 80 %, 2.77 vs 4.15 ms at 50 %,
 //     4.1 vs 7.9 ms dense), loses at 90 % -> share >= 1.3;
 //   batch tile of 8: wins at 50 % (1.02 vs 1.16 ms), loses at 80 % -> share >= 1.7;
 //   batch tile of 4: wins at every density tried (0.26 vs 0.37 ms at 90 %).

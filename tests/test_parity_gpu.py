@@ -212,6 +212,8 @@ CONV_CASES = [
     (4, 8, 16, 12, 12, 3, 1, 1, 1), (32, 16, 24, 14, 14, 3, 1, 1, 1), (3, 5, 7, 9, 11, 3, 1, 0, 1),
     (8, 16, 8, 10, 10, 1, 1, 0, 1), (2, 6, 6, 13, 9, 5, 1, 2, 1), (4, 8, 8, 12, 12, 3, 2, 1, 1),
     (5, 4, 6, 11, 11, 3, 1, 2, 2), (16, 32, 32, 8, 8, 3, 1, 1, 1), (1, 3, 4, 6, 6, 3, 1, 1, 1),
+    # more work units than SMs with a last wave under half full: the tail goes out as half-height tiles
+    (32, 8, 64, 56, 56, 3, 1, 1, 1), (32, 8, 64, 54, 50, 3, 1, 1, 1),
 ]
 
 
