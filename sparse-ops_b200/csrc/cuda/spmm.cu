@@ -156,7 +156,7 @@ spmm_gather_sub(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
                 uint32_t m, uint32_t pitch,
                 const float* __restrict__ X, uint32_t C, uint64_t ldx,
-                const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy)
+                const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy, bool prefetch_slabs)
 {
     constexpr int RPW = 32 / LPR;
     const int lane = threadIdx.x & 31;
@@ -175,18 +175,38 @@ spmm_gather_sub(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     const uint32_t* __restrict__ k = idx + (size_t)row * pitch;
 
     constexpr int NB = LPR * BM;
+    // (w, idx) of the next batch are fetched while this batch's gathers are in flight, so a batch
+    // costs one memory round trip, not two (the kernel is bound by this per-row chain).
+    float wn[BM];
+    uint32_t kn[BM];
+    auto fetch = [&](uint32_t j) {
+#pragma unroll
+        for (int h = 0; h < BM; ++h) {
+            wn[h] = 0.0f;
+            kn[h] = 0;
+            if (j + h * LPR + sl < nn) {
+                wn[h] = __ldg(w + j + h * LPR + sl);
+                kn[h] = __ldg(k + j + h * LPR + sl);
+            }
+        }
+    };
+    fetch(0);
+    // The row's slabs are touched 32 entries at a time, one DRAM round trip each when they are not
+    // in L2 yet: ask for all of the row's lines now so that the later batches find them in L2.
+    // Only when the whole matrix fits L2 with room to spare (the caller decides): otherwise the
+    // lines would be evicted again before their batch comes up.
+    if (prefetch_slabs) {
+        for (uint32_t j = NB + sl * 32; j < nn; j += LPR * 32) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(w + j));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(k + j));
+        }
+    }
     for (uint32_t j0 = 0; j0 < nmax; j0 += NB) {
         float wl[BM];
         uint32_t kl[BM];
 #pragma unroll
-        for (int h = 0; h < BM; ++h) {
-            wl[h] = 0.0f;
-            kl[h] = 0;
-            if (j0 + h * LPR + sl < nn) {
-                wl[h] = __ldg(w + j0 + h * LPR + sl);
-                kl[h] = __ldg(k + j0 + h * LPR + sl);
-            }
-        }
+        for (int h = 0; h < BM; ++h) { wl[h] = wn[h]; kl[h] = kn[h]; }
+        if (j0 + NB < nmax) fetch(j0 + NB);
         const uint32_t cnt = j0 < nn ? min((uint32_t)NB, nn - j0) : 0u;      // entries of this lane's row in the batch
         float wt[NB];
         float4 xv[NB];
@@ -364,15 +384,18 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
         // (batch 32 forward of a 4096-wide MLP: 0.165 -> 0.106 ms; with 16 lanes per row it was slower).
         static const int deep_env = [] { const char* v = getenv("SPX_SPMM_SUB_DEEP"); return v ? atoi(v) : -1; }();
         const bool deep = deep_env >= 0 ? deep_env != 0 : warps < (uint64_t)sm_count(e->device) * 16;
+        // L2 prefetch of each row's slabs at row start: 4096-wide MLP at batch 32, 0.102 -> 0.096 ms;
+        // a 134 MB matrix (larger than L2) got 16 % slower with it, hence the size limit.
+        const bool pf = e->nnz_total * 8 <= (32ull << 20);
         if (lpr == 8 && deep)
             spmm_gather_sub<8, 4, 1><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                X, C, ldx, bias, act, out, ldy);
+                                                                X, C, ldx, bias, act, out, ldy, pf);
         else if (lpr == 8)
             spmm_gather_sub<8, 2, 4><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                X, C, ldx, bias, act, out, ldy);
+                                                                X, C, ldx, bias, act, out, ldy, pf);
         else
             spmm_gather_sub<16, 1, 4><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
-                                                                 X, C, ldx, bias, act, out, ldy);
+                                                                 X, C, ldx, bias, act, out, ldy, pf);
         SPX_LAUNCH_CHECK("spmm_gather_sub");
     } else if (vec_ok) {
         const int nv = gather_nv(e->n, C);
