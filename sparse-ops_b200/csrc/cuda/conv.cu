@@ -634,28 +634,30 @@ static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float
     return launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)units, in, bias, act, out, s);
 }
 
-// Row-block-merged path.  Taken when K fits the builder's set and the expected number of rows per
-// union column, 4 d / (1 - (1 - d)^4) for density d, pays for the mask tests.  Measured against
-// conv_pf_tile_kernel on 256 -> 256 channels, 3 x 3, 56 x 56:
-//   batch a multiple of 16: tiles of 16 entries (faster than 32: twice the channels per staged
-//     chunk); wins from 80 % sparsity down (1.69 vs 1.89 ms at 80 %, 2.77 vs 4.15 ms at 50 %,
-//     4.1 vs 7.9 ms dense), loses at 90 % -> share >= 1.3;
-//   batch tile of 8: wins at 50 % (1.02 vs 1.16 ms), loses at 80 % -> share >= 1.7;
-//   batch tile of 4: wins at every density tried (0.26 vs 0.37 ms at 90 %).
-// Other batch sizes keep the per-row kernel with its wider batch tile.  SPX_CONV_RBM=0 turns the
-// path off, SPX_CONV_RBM_MIN_SHARE overrides the three thresholds.  Returns -1 when not taken.
+// Row-block-merged path.  Taken whenever K fits the builder's set and the batch tile is 16 (any
+// batch that is a multiple of 16), 8 or 4.  Measured against conv_pf_tile_kernel on 256 -> 256
+// channels, 3 x 3, 56 x 56 (ms, merged vs per-row):
+//   batch 32 (tiles of 16; faster than tiles of 32: twice the channels per staged chunk):
+//     dense 4.1 vs 7.9, 50 % sparse 2.77 vs 4.15, 80 % 1.69 vs 1.89, 90 % 1.07 vs 1.13,
+//     95 % 0.69 vs 0.75, 99 % 0.35 vs 0.44;
+//   batch 8: 80 % 0.51 vs 0.57, 90 % 0.33 vs 0.40, 99 % 0.12 vs 0.25;   batch 4: 90 % 0.26 vs 0.37.
+// The fewer operand loads pay at high density; at low density the win comes from a CTA covering 64
+// output channels per staged chunk instead of 16 or 32.  Other batch sizes (tiles of 12, 20, 24,
+// 28) keep the per-row kernel with its wider batch tile.  SPX_CONV_RBM=0 turns the path off;
+// SPX_CONV_RBM_MIN_SHARE=x requires an expected 4 d / (1 - (1 - d)^4) >= x rows per union column
+// (density d).  Returns -1 when not taken.
 static int launch_conv_rbm_tile(spx_ell* e, const ConvParams& p, uint32_t BT, const float* in, const float* bias,
                                 int act, float* out, cudaStream_t s)
 {
     static const int enabled = [] { const char* v = getenv("SPX_CONV_RBM"); return v ? atoi(v) : 1; }();
     static const double share_env = [] { const char* v = getenv("SPX_CONV_RBM_MIN_SHARE"); return v ? atof(v) : -1.0; }();
-    if (!enabled || e->n > kRbmMaxK || e->m < kRbmRows || e->max_nnz == 0) return -1;
+    // fewer than 8 row blocks would leave most of the CTA's 16 warps without work
+    if (!enabled || e->n > kRbmMaxK || e->m < 8 * kRbmRows - 3 || e->max_nnz == 0) return -1;
     const uint32_t bt = p.B % 16 == 0 ? 16 : BT;       // BT: the per-row kernel's batch tile for this batch
     if (bt != 16 && bt != 8 && bt != 4) return -1;
     const double d = (double)e->nnz_total / ((double)e->m * e->n);
     const double share = d >= 1.0 ? (double)kRbmRows : kRbmRows * d / (1.0 - std::pow(1.0 - d, (double)kRbmRows));
-    const double min_share = share_env >= 0.0 ? share_env : bt == 16 ? 1.3 : bt == 8 ? 1.7 : 1.0;
-    if (share < min_share) return -1;
+    if (share_env >= 0.0 && share < share_env) return -1;
     TileParams tp{};
     tp.c = p;
     if (bt == 16) return launch_rbm_qb<4>(e, tp, in, bias, act, out, s);

@@ -214,6 +214,8 @@ CONV_CASES = [
     (5, 4, 6, 11, 11, 3, 1, 2, 2), (16, 32, 32, 8, 8, 3, 1, 1, 1), (1, 3, 4, 6, 6, 3, 1, 1, 1),
     # more work units than SMs with a last wave under half full: the tail goes out as half-height tiles
     (32, 8, 64, 56, 56, 3, 1, 1, 1), (32, 8, 64, 54, 50, 3, 1, 1, 1),
+    # a last block of output channels that is not full (38 = 9 blocks of 4 + 2), batch tiles of 16 / 8 / 4
+    (16, 6, 38, 10, 10, 3, 1, 1, 1), (8, 6, 38, 10, 10, 3, 1, 1, 1), (4, 6, 38, 10, 10, 3, 1, 1, 1),
 ]
 
 
