@@ -10,7 +10,8 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Kernel
  *     entry points only enqueue work; they do not synchronise.
  *   - A handle may be used from several host threads for kernel launches, but entry points
- *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, the NCHW layout,
+ *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, its NCHW layout
+ *     and batch sizes that are not a multiple of 4,
  *     the first spx_spmv of a handle with n > 51200, the *_host calls) must not run concurrently
  *     on the same handle.
  *   - There is no CPU fallback: without a usable CUDA device every compute entry point
