@@ -101,6 +101,8 @@ SPMM_CASES = [
     (10, 10, 1, 1.0), (10, 10, 10, 0.5), (10, 10, 10, 0.1), (20, 20, 10, 0.8), (100, 100, 10, 0.8),
     (1000, 1000, 10, 0.9), (500, 500, 10, 0.95), (2000, 2000, 10, 0.7), (3000, 3000, 10, 0.6),
     (300, 700, 256, 0.1), (257, 129, 260, 0.2), (64, 4096, 128, 0.1), (513, 300, 36, 0.15), (40, 50, 1024, 0.3),
+    # widths that are not a multiple of 4: the scalar kernel with 64- and 256-column panels
+    (300, 200, 130, 0.2), (129, 333, 255, 0.1), (70, 90, 513, 0.3),
 ]
 
 
