@@ -214,3 +214,40 @@ def test_python_onnx_reader_round_trip():
     assert conv["nodes"][0]["attrs"]["strides"] == [2, 2] and conv["nodes"][0]["attrs"]["pads"] == [1, 1, 1, 1]
     with pytest.raises(ValueError):
         ow.read_model(ow.mlp_model(Ws, bs, ["Relu", None], 4)[:-7])      # truncated file
+
+
+def test_python_onnx_reader_random_graphs():
+    """Writer -> reader round trip over random small graphs: node order, operand names, integer
+    attributes (negative values too) and tensors of any rank survive."""
+    import onnx_wire as ow
+    rng = np.random.default_rng(11)
+    for trial in range(25):
+        n_nodes = int(rng.integers(1, 6))
+        inits, nodes, want = [], [], []
+        prev = "input"
+        for i in range(n_nodes):
+            op = str(rng.choice(["Gemm", "MatMul", "Relu", "Conv", "Identity"]))
+            shape = tuple(int(d) for d in rng.integers(1, 5, size=int(rng.integers(1, 5))))
+            t = rng.standard_normal(shape).astype(np.float32)
+            name = f"t{trial}_{i}"
+            inits.append(ow.tensor(name, t, packed_float_data=bool(rng.integers(0, 2))))
+            attrs = {"a": int(rng.integers(-5, 6)), "ks": [int(v) for v in rng.integers(0, 9, size=3)]}
+            nodes.append(ow.node(op, [prev, name], [f"o{i}"], [ow.attr_int("a", attrs["a"]), ow.attr_ints("ks", attrs["ks"])]))
+            want.append((op, [prev, name], [f"o{i}"], attrs, name, t))
+            prev = f"o{i}"
+        m = ow.read_model(ow.model(nodes, inits, ("input", (2, 3)), (prev, (2, 3))))
+        assert len(m["nodes"]) == n_nodes
+        for nd, (op, ins, outs, attrs, name, t) in zip(m["nodes"], want):
+            assert nd["op_type"] == op and nd["input"] == ins and nd["output"] == outs and nd["attrs"] == attrs
+            got = m["initializers"][name]
+            assert got.shape == t.shape and np.array_equal(got, t)
+
+
+def test_conv_workload_density_parameter():
+    import workloads as wl
+    d = wl.cfg4(0.1, layers=1, density=0.5)
+    w = d["weights"][0]
+    frac = np.count_nonzero(w) / w.size
+    assert 0.35 < frac < 0.65
+    d2 = wl.cfg4(0.1, layers=1)                     # default: 80 % sparse
+    assert 0.1 < np.count_nonzero(d2["weights"][0]) / d2["weights"][0].size < 0.3
