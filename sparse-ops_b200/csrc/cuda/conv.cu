@@ -744,6 +744,23 @@ static int launch_conv_pf_tile(spx_ell* e, const ConvParams& p, const float* in,
     return -1;
 }
 
+// Batch size the tiled kernels run at: B rounded up to a multiple of 4, or further up to a multiple
+// of 16 when that is cheaper.  Cost per batch entry by the batch tile the kernels would pick,
+// measured on 256 -> 256 channels, 3 x 3, 56 x 56, 80 % sparse (ms per entry): tile 16 (merged
+// kernel) 0.056, tile 8 (merged) 0.064, tile 4 (merged) 0.094, per-row tiles of 12 / 20 / 24 / 28:
+// 0.064 / 0.069 / 0.066 / 0.068.  So 28 runs as 32 (1.83 against 1.91 ms with the widening passes) and 44 as 48 (about 2.7 against
+// 4.1 ms), while 12, 20, 24 and 36 stay as they are.
+static uint32_t padded_batch(uint32_t B)
+{
+    const uint32_t b4 = round_up(B, 4u), b16 = round_up(B, 16u);
+    if (b4 == b16) return b4;
+    uint32_t tile = 0;
+    for (uint32_t c = 32; c >= 4; c -= 4) if (b4 % c == 0) { tile = c; break; }
+    static const double per_entry[9] = {0, 0.094, 0.064, 0.064, 0.056, 0.069, 0.066, 0.068, 0.056};
+    const double as_is = b4 * per_entry[tile / 4], widened = b16 * 0.056 * 1.03;
+    return widened < as_is ? b16 : b4;
+}
+
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                   const float* bias, int act, float* out, cudaStream_t s)
 {
@@ -758,11 +775,12 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     // form in per-handle scratch and the result is converted back:
     //   NCHW (B > 1; one NCHW image already is [C,H,W,1]): transpose in, transpose out - two extra
     //     streaming passes over input and output (about 5 % of the kernel's time at 256 channels);
-    //   B not a multiple of 4: the batch dimension is widened with zero entries and narrowed again
+    //   B not a multiple of 4 (or cheaper at the next multiple of 16, see padded_batch): the batch
+    //     dimension is widened with zero entries and narrowed again
     //     (256 -> 256 channels, 56 x 56: batch 3 takes 0.4 ms this way against 1.2 ms with the general
     //     kernel, batch 1 0.4 against 0.43 ms).
     // Arithmetic per output element is unchanged in both cases.
-    const uint32_t B4 = round_up(B, 4u);
+    const uint32_t B4 = padded_batch(B);
     ConvParams p4 = p;
     p4.B = B4;
     if (e->r && e->cols_ascending && pf_tile_covers(p4)) {
