@@ -748,8 +748,8 @@ static int launch_conv_pf_tile(spx_ell* e, const ConvParams& p, const float* in,
 // of 16 when that is cheaper.  Cost per batch entry by the batch tile the kernels would pick,
 // measured on 256 -> 256 channels, 3 x 3, 56 x 56, 80 % sparse (ms per entry): tile 16 (merged
 // kernel) 0.056, tile 8 (merged) 0.064, tile 4 (merged) 0.094, per-row tiles of 12 / 20 / 24 / 28:
-// 0.064 / 0.069 / 0.066 / 0.068.  So 28 runs as 32 (1.83 against 1.91 ms with the widening passes) and 44 as 48 (about 2.7 against
-// 4.1 ms), while 12, 20, 24 and 36 stay as they are.
+// 0.064 / 0.069 / 0.066 / 0.068.  So 28 runs as 32 (1.83 against 1.91 ms with the widening passes)
+// and 44 as 48 (about 2.7 against 4.1 ms), while 12, 20, 24 and 36 stay as they are.
 static uint32_t padded_batch(uint32_t B)
 {
     const uint32_t b4 = round_up(B, 4u), b16 = round_up(B, 16u);
