@@ -233,6 +233,87 @@ spmm_gather_sub(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// spmm_gather_half: 64 < C <= 128.  With a full warp per row a lane would own one float4 and the
+// per-entry work that does not scale with the width (two shuffles, the row address, the loop)
+// would be spread over 4 FMAs; here 16 lanes share a row and own two float4 each, a warp carries
+// two neighbouring rows of the sorted schedule, and every shuffle / address / load instruction
+// serves both rows, as in spmm_gather_vec<2> at C = 256.  Same chain per output element.
+// ---------------------------------------------------------------------------------------
+template <int G, int MINB>
+__global__ void __launch_bounds__(kGatherWarps * 32, MINB)
+spmm_gather_half(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+                 const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                 uint32_t m, uint32_t pitch,
+                 const float* __restrict__ X, uint32_t C, uint64_t ldx,
+                 const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy)
+{
+    const int lane = threadIdx.x & 31;
+    const int sl = lane & 15;
+    const uint32_t slot = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+    const bool live = slot < m;
+    const uint32_t row = live ? __ldg(row_order + slot) : 0u;
+    const uint32_t c0 = 4u * sl;
+    bool on[2];
+#pragma unroll
+    for (int v = 0; v < 2; ++v) on[v] = live && (c0 + 64u * v) < C;
+
+    const float b = (live && bias) ? __ldg(bias + row) : 0.0f;
+    float4 acc[2];
+#pragma unroll
+    for (int v = 0; v < 2; ++v) acc[v] = make_float4(b, b, b, b);
+    const uint32_t nn = live ? __ldg(nnz + row) : 0u;
+    const uint32_t nmax = __reduce_max_sync(0xffffffffu, nn);       // the warp runs to its longer row
+    const float* __restrict__ w = Wd + (size_t)row * pitch;
+    const uint32_t* __restrict__ k = idx + (size_t)row * pitch;
+
+    for (uint32_t j0 = 0; j0 < nmax; j0 += 16) {
+        float wl = 0.0f;
+        uint32_t kl = 0;
+        if (j0 + sl < nn) {                     // 64-byte slab reads per half warp
+            wl = __ldg(w + j0 + sl);
+            kl = __ldg(k + j0 + sl);
+        }
+        const uint32_t cnt = j0 < nn ? min(16u, nn - j0) : 0u;      // entries of this lane's row in the batch
+        const uint32_t cmax = min(16u, nmax - j0);
+        for (uint32_t t0 = 0; t0 < cmax; t0 += G) {
+            float wt[G];
+            float4 xv[G][2];
+#pragma unroll
+            for (int u = 0; u < G; ++u) {
+                wt[u] = __shfl_sync(0xffffffffu, wl, (t0 + u) & 15, 16);
+                const uint32_t kt = __shfl_sync(0xffffffffu, kl, (t0 + u) & 15, 16);
+                const float* xr = X + (size_t)kt * ldx + c0;
+                const bool have = (t0 + u) < cnt;
+#pragma unroll
+                for (int v = 0; v < 2; ++v)
+                    xv[u][v] = (have && on[v]) ? ldg4(xr + 64 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < G; ++u) {
+                if ((t0 + u) < cnt) {
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) fma4(acc[v], wt[u], xv[u][v]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+        if (on[v]) {
+            float4 o = acc[v];
+            if (act != SPX_ACT_NONE) {
+                o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
+                o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
+            }
+            const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 64 * v;
+#pragma unroll
+            for (int g = 0; g < kMaxPeers; ++g)
+                if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+        }
+    }
+}
+
 // Scalar variant for C % 4 != 0 or unaligned operands: lane owns columns c0 + 32*v + lane.
 template <int NV>
 __global__ void __launch_bounds__(kGatherWarps * 32)
@@ -370,6 +451,7 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
         out.p[g] = Ys[g];
         aligned = aligned && (reinterpret_cast<uintptr_t>(Ys[g]) & 15) == 0;
     }
+    static const int half_env = [] { const char* v = getenv("SPX_SPMM_HALF"); return v ? atoi(v) : 1; }();
     const bool vec_ok = (C % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
                         ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && aligned;
     if (vec_ok && C <= 64) {
@@ -397,6 +479,14 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
             spmm_gather_sub<16, 1, 4><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
                                                                  X, C, ldx, bias, act, out, ldy, pf);
         SPX_LAUNCH_CHECK("spmm_gather_sub");
+    } else if (vec_ok && C <= 128 && half_env) {
+        const uint32_t warps = (e->m + 1) / 2;
+        uint32_t wpb = 8;
+        while (wpb > 1 && (uint64_t)((warps + wpb - 1) / wpb) < (uint64_t)sm_count(e->device) * 8) wpb >>= 1;
+        const uint32_t blocks = (warps + wpb - 1) / wpb;
+        spmm_gather_half<4, 4><<<blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                          X, C, ldx, bias, act, out, ldy);
+        SPX_LAUNCH_CHECK("spmm_gather_half");
     } else if (vec_ok) {
         const int nv = gather_nv(e->n, C);
         // A row is one dependent chain of gathers, G rows of X per round trip to L2 (about a
