@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the other configurations in the default run")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of the results with the CPU oracle")
     return ap.parse_args()
 
 
@@ -79,12 +80,33 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def recorded_traffic(kernel: str, workload: str):
-    """DRAM bytes per launch from the committed ncu summary, if one exists for this workload."""
+def recorded_traffic(kernel: str, args, world: int):
+    """DRAM bytes per launch from the committed ncu summary -- only where the profiled launch is the
+    timed launch: the named workload at its full size on one GPU.  Anything else (a rank's shard, a
+    scaled or resized case) has no measured traffic and reports null."""
+    if world != 1 or args.scale != 1.0 or args.rows or args.cols or args.batch:
+        return None
     try:
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-            return json.load(f).get(f"{kernel}:{workload}")
+            key = f"{kernel}:{args.workload}"
+        if args.workload == "cfg2_spmv":
+            key += f":{args.size}:{args.sparsity}"
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(key)
     except Exception:
+        return None
+
+
+def load_probe():
+    """bench_l2_gather_probe of sparse-ops_b200/libspx_bench_probe.so (bench equipment), or None."""
+    try:
+        dll = ctypes.CDLL(os.path.join(PKG, "libspx_bench_probe.so"))
+        fn = dll.bench_l2_gather_probe
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p,
+                       ctypes.POINTER(ctypes.c_uint64)]
+        return fn
+    except (OSError, AttributeError):
         return None
 
 
@@ -221,6 +243,63 @@ def build_workload(args, rank: int, world: int):
     raise SystemExit(f"unknown workload {w}")
 
 
+def sample_rows(rowptr, k_long=6, k_spread=26):
+    """Row ids to check: the longest rows of the range and an even spread over the rest."""
+    counts = np.diff(rowptr.astype(np.int64))
+    m = len(counts)
+    if m == 0:
+        return np.zeros(0, np.int64)
+    longest = np.argsort(counts, kind="stable")[::-1][:k_long]
+    spread = np.linspace(0, m - 1, num=min(m, k_spread)).astype(np.int64)
+    return np.unique(np.concatenate([longest, spread]))
+
+
+def oracle_rows_spmm(csr, rows, n, X, bias):
+    """The oracle's SpMM (one FMA per stored entry, in order, from the bias) on the given rows."""
+    import oracle
+    import workloads as wl
+    rowptr, col, val = csr
+    cnt = np.diff(rowptr.astype(np.int64))[rows]
+    rp = np.zeros(len(rows) + 1, np.uint64)
+    rp[1:] = np.cumsum(cnt)
+    cc = np.concatenate([col[int(rowptr[i]):int(rowptr[i + 1])] for i in rows]) if len(rows) else np.zeros(0, np.uint32)
+    vv = np.concatenate([val[int(rowptr[i]):int(rowptr[i + 1])] for i in rows]) if len(rows) else np.zeros(0, np.float32)
+    Wd, idx, nnz = wl.csr_to_ell(len(rows), rp, cc, vv)
+    E = oracle.EllArrays(len(rows), n, Wd.shape[1], Wd, idx, nnz)
+    orc = oracle.Oracle()
+    return E, orc, orc.spmm(E, X, None if bias is None else bias[rows])
+
+
+def bits_equal(a, b) -> bool:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    return a.shape == b.shape and bool(np.array_equal(a.view(np.uint32), b.view(np.uint32)))
+
+
+def config_of(args, wk, world: int, local_nnz: int):
+    """The `config` object of the JSON line -- the same for the product arm and the reference arm --
+    together with the L2 protocol it describes: (config, copies of the operands, flush needed)."""
+    kind = wk["kind"]
+    if kind == "spmm":
+        working_set = (wk["n"] * wk["C"] + wk["rows"] * wk["C"]) * 4 + 8 * local_nnz
+    elif kind == "spmv":
+        working_set = 8 * local_nnz + 4 * wk["n"]
+    elif kind == "conv":
+        working_set = 2 * (wk["B"] // world) * wk["C"] * wk["H"] * wk["W"] * 4
+    else:
+        working_set = 64 << 20
+    ncopies = rotation_copies(working_set, world) if kind in ("spmm", "spmv") else 1
+    rotating = ncopies > 1
+    need_flush = working_set < (256 << 20) and not rotating
+    cfg = {"workload": args.workload, "desc": wk["desc"],
+           "l2": (f"{ncopies} rotating copies of the operands ({ncopies * working_set >> 20} MiB > L2), launches back to back"
+                  if rotating else "flushed between timed iterations (512 MiB write)" if need_flush
+                  else "inputs larger than L2"),
+           "sharding": "rows of E split over ranks, X replicated, Y row-sharded" if kind in ("spmm", "spmv")
+           else ("row-sharded layers + all-gather" if args.tp else "batch-sharded, no collective")}
+    return cfg, ncopies, need_flush
+
+
 def rotation_copies(working_set: int, world: int) -> int:
     """Operands that fit L2 are replicated so that consecutive timed launches never touch the same
     copy before it has been evicted (total well above the 126 MB L2); larger operands need one copy."""
@@ -256,8 +335,21 @@ def cpu_engine():
     return oracle.Oracle(), "port"
 
 
-def cpu_sample_runner(args, wk, budget_rows=None):
-    """Builds the bounded CPU sample of this workload.  Returns (run_fn, work_fraction, text)."""
+def host_memory_available() -> int:
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available)
+    except Exception:
+        return 8 << 30
+
+
+def cpu_sample_runner(args, wk, fraction=None):
+    """Builds the bounded CPU sample of this workload.  Returns (run_fn, work_fraction, kind, text).
+
+    fraction (SpMM / SpMV): share of the matrix's nonzeros the sample should hold, taken as its
+    first rows; None = about 4 GFLOP of work (a stable timing in well under a second).  1.0 runs the
+    whole matrix.  The share is cut down to what the host's free memory holds (the reference keeps
+    three padded m x r arrays: Wd, idx and its Xt scratch, next to the two this script builds)."""
     import oracle
     import workloads as wl
     eng, kind = cpu_engine()
@@ -273,12 +365,22 @@ def cpu_sample_runner(args, wk, budget_rows=None):
         rows = wk["rows"]
         total_nnz = int(rowptr[-1])
         take = rows
-        if wk["kind"] == "spmm":
-            # about 4 GFLOP of the same matrix: enough for a stable CPU timing, seconds not minutes
-            target = 4e9 / (2.0 * wk["C"])
-            if total_nnz > target:
-                take = max(1, int(np.searchsorted(rowptr, target)))
+        if fraction is None:
+            if wk["kind"] == "spmm":
+                # about 4 GFLOP of the same matrix: enough for a stable CPU timing, seconds not minutes
+                target = 4e9 / (2.0 * wk["C"])
+                if total_nnz > target:
+                    take = max(1, int(np.searchsorted(rowptr, target)))
+            elif total_nnz > 64e6:                  # SpMV: at most 64 M nonzeros (0.5 GB of matrix)
+                take = max(1, int(np.searchsorted(rowptr, 64e6)))
+        elif fraction < 1.0:
+            take = max(1, int(np.searchsorted(rowptr, fraction * total_nnz)))
         take = min(take, rows)
+        r_max = int(np.diff(rowptr[:take + 1].astype(np.int64)).max()) if take else 0
+        budget = host_memory_available() // 2
+        per_row = max(1, r_max) * 4 * 5 + wk["C"] * 4
+        if take * per_row > budget:
+            take = max(1, budget // per_row)
         sub = (rowptr[:take + 1].copy(), col[:int(rowptr[take])], val[:int(rowptr[take])])
         E = make_ell(*sub, take, wk["n"])
         frac = float(rowptr[take]) / max(1, total_nnz)
@@ -291,7 +393,8 @@ def cpu_sample_runner(args, wk, budget_rows=None):
             x = wk["x"]
             y = np.empty(take, np.float32)
             run = (lambda: eng.matvec(E, x, bias, out=y)) if is_ref else (lambda: eng.spmv(E, x, bias))
-        return run, frac, kind, f"rows 0..{take - 1} of {rows} of the same matrix ({frac:.3f} of the nonzeros), full dense operand"
+        what = "the whole matrix" if take == rows else f"rows 0..{take - 1} of {rows} of the same matrix ({frac:.3f} of the nonzeros)"
+        return run, frac, kind, what + ", full dense operand"
     if wk["kind"] == "mlp":
         import onnx_wire
         import tempfile
@@ -350,17 +453,23 @@ def cpu_sample_runner(args, wk, budget_rows=None):
 
 
 def time_cpu(run, repeats, warmup=1, budget_s=25.0):
+    """Median wall time of `repeats` runs after `warmup` untimed ones; both are cut short when the
+    budget (seconds, warm-up included) runs out, so the leg always ends."""
+    t_start = time.perf_counter()
+    done_warm = 0
     for _ in range(warmup):
         run()
+        done_warm += 1
+        if time.perf_counter() - t_start > budget_s / 3:
+            break
     ts = []
-    t_start = time.perf_counter()
     for _ in range(max(1, repeats)):
         t0 = time.perf_counter()
         run()
         ts.append(time.perf_counter() - t0)
         if time.perf_counter() - t_start > budget_s:
             break
-    return float(np.median(ts)), len(ts)
+    return float(np.median(ts)), len(ts), done_warm
 
 
 def metric_of(wk, args):
@@ -407,26 +516,31 @@ def to_value(wk, job_bytes, seconds):
 
 # ------------------------------------------------------------------------------------------------
 def run_reference_arm(args):
+    """The reference's own CPU implementation on the host cores.  SpMM / SpMV run the WHOLE matrix
+    per step where the host's memory holds the reference's padded arrays (config 5: about 11 GB),
+    otherwise the largest share that fits, scaled by its share of the nonzeros and labelled so."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wk = build_workload(args, 0, 1)
     nnz_total = int(wk["csr"][0][-1]) if "csr" in wk else 0
     job_bytes, job_flops = job_bytes_flops(wk, nnz_total)
-    run, frac, kind, sample = cpu_sample_runner(args, wk)
-    med, reps = time_cpu(run, args.steps, warmup=max(1, min(args.warmup, 2)))
+    run, frac, kind, sample = cpu_sample_runner(args, wk, fraction=1.0)
+    med, reps, warm = time_cpu(run, args.steps, warmup=args.warmup, budget_s=240.0)
     sec_full = med / frac
     metric, unit = metric_of(wk, args)
     value = to_value(wk, job_bytes, sec_full)
     cores = host_cores()
+    scaled = "" if frac == 1.0 else f", scaled by 1/{frac:.4f} to the whole job"
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": reps,
-        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": sec_full * 1e3, "higher_is_better": True,
+        "warmup": warm, "ms_per_step": sec_full * 1e3, "measured_ms_per_sample": med * 1e3, "sample_fraction": frac,
+        "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": args.workload, "desc": wk["desc"]},
+        "data": "synthetic", "config": config_of(args, wk, 1, nnz_total)[0],
         "gflops": job_flops / sec_full / 1e9,
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind,
-                         "sample": sample + f"; median of {reps} runs of {med * 1e3:.2f} ms, scaled by 1/{frac:.4f} to the whole job"},
+                         "sample": sample + f"; median of {reps} runs of {med * 1e3:.2f} ms" + scaled},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -475,6 +589,9 @@ def measure(args, c):
     e2e_step = None
     ag_step = None
     fused_step = None
+    e2e_phases = None
+    checks = []                 # (what, rows compared, ok) filled by run_checks after the timed regions
+    run_checks = None
 
     if kind in ("spmm", "spmv"):
         rowptr, col, val = wk["csr"]
@@ -488,8 +605,7 @@ def measure(args, c):
             C = wk["C"]
             dX = torch.from_numpy(wk["X"]).to(dev)
             dY = torch.empty((wk["rows"], C), device=dev, dtype=torch.float32)
-            working_set = (wk["n"] * C + wk["rows"] * C) * 4 + 8 * ell.nnz_total
-            ncopies = rotation_copies(working_set, world)
+            config, ncopies, need_flush = config_of(args, wk, world, ell.nnz_total)
             ells = [ell] + [lib.ell_create_csr(wk["rows"], wk["n"], rowptr, col, val) for _ in range(ncopies - 1)]
             dXs = [dX] + [dX.clone() for _ in range(ncopies - 1)]
             dYs = [dY] + [torch.empty_like(dY) for _ in range(ncopies - 1)]
@@ -501,21 +617,49 @@ def measure(args, c):
             hX = torch.from_numpy(wk["X"]).pin_memory()
             hY = torch.empty((wk["rows"], C), dtype=torch.float32).pin_memory()
             hB = None if wk["bias"] is None else torch.from_numpy(wk["bias"]).pin_memory()
-            h2d = hX.numel() * 4 + (0 if hB is None else hB.numel() * 4)
             d2h = hY.numel() * 4
+            rows_lo = wk["row0"]
 
-            def e2e_step():
-                lib.spx_spmm_host(ell.h, hX.data_ptr(), C, 0 if hB is None else hB.data_ptr(), sx.ACT_NONE, hY.data_ptr())
-            if world > 1:
+            def check_rows_against_oracle(Ydev_rows, local_rows, what):
+                """Ydev_rows: device tensor whose row i is the output row local_rows[i] of this rank."""
+                _, _, want = oracle_rows_spmm(wk["csr"], local_rows, wk["n"], wk["X"], wk["bias"])
+                ok = bits_equal(Ydev_rows.cpu().numpy(), want)
+                checks.append((what, len(local_rows), ok))
+            if not args.no_check:
+                picked = sample_rows(rowptr)
+                pick_dev = torch.from_numpy(picked).to(dev)
+            if world == 1:
+                h2d = hX.numel() * 4 + (0 if hB is None else hB.numel() * 4)
+
+                def e2e_step():
+                    lib.spx_spmm_host(ell.h, hX.data_ptr(), C, 0 if hB is None else hB.data_ptr(), sx.ACT_NONE, hY.data_ptr())
+            else:
+                import ctypes as Ct
+                idb = [None]
+                if rank == 0:
+                    ub = Ct.create_string_buffer(sx.UNIQUE_ID_BYTES)
+                    lib.spx_comm_unique_id(ub)
+                    idb = [ub.raw]
+                dist.broadcast_object_list(idb, src=0)
+                fcomm = Ct.c_void_p()
+                lib.spx_comm_create(rank, world, idb[0], Ct.byref(fcomm))
+                # end to end on host buffers: every rank copies its block of X's rows over PCIe, the
+                # ranks rebuild X over NVLink, multiply, and copy their own rows of Y back
+                per_x = -(-wk["n"] // world)
+                h2d = max(0, min(wk["n"], (rank + 1) * per_x) - min(wk["n"], rank * per_x)) * C * 4 + (0 if hB is None else hB.numel() * 4)
+                e2e_phases = (Ct.c_float * 4)()
+
+                def e2e_step():
+                    lib.spx_spmm_host_sharded(fcomm, ell.h, hX.data_ptr(), C, 0 if hB is None else hB.data_ptr(), sx.ACT_NONE,
+                                              hY.data_ptr(), e2e_phases)
                 Yfull = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
                 Yslab = Yfull[wk["row0"]:wk["row0"] + wk["rows"]]
 
                 def ag_step():
                     ell.spmm(dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, Yslab.data_ptr(), C, stream)
-                    dist.all_gather_into_tensor(Yfull, Yslab)
+                    lib.spx_allgather_rows(fcomm, Yfull.data_ptr(), wk["rows"], C, stream)
                 # the same exchange fused into the epilogue: stores into every rank's full buffer
                 # (own + peers' buffers opened over IPC), followed by a stream-ordered barrier
-                import ctypes as Ct
                 fbuf = Ct.c_void_p()
                 lib.spx_malloc(Ct.byref(fbuf), wk["m"] * C * 4)
                 hnd = Ct.create_string_buffer(sx.IPC_HANDLE_BYTES)
@@ -531,24 +675,42 @@ def measure(args, c):
                         lib.spx_ipc_open(hs[g_], Ct.byref(pp))
                         plist.append(pp.value)
                 parr = (Ct.c_void_p * world)(*plist)
-                idb = [None]
-                if rank == 0:
-                    ub = Ct.create_string_buffer(sx.UNIQUE_ID_BYTES)
-                    lib.spx_comm_unique_id(ub)
-                    idb = [ub.raw]
-                dist.broadcast_object_list(idb, src=0)
-                fcomm = Ct.c_void_p()
-                lib.spx_comm_create(rank, world, idb[0], Ct.byref(fcomm))
 
                 def fused_step():
                     lib.spx_spmm_bcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, parr, world,
                                        wk["row0"], C, stream)
                     lib.spx_comm_barrier(fcomm, stream)
+
+            def run_checks():
+                """After the timed regions: sampled rows of every result buffer against the oracle.
+                Gathered buffers are also checked on rows another rank computed."""
+                if args.no_check:
+                    return
+                torch.cuda.synchronize()
+                check_rows_against_oracle(dYs[rot[0]][pick_dev], picked, "device-resident Y")
+                if e2e_step is not None and not args.no_e2e:
+                    check_rows_against_oracle(hY[torch.from_numpy(picked)], picked, "host-buffer Y")
+                if world > 1:
+                    import workloads as wl
+                    nb = (rank + 1) % world                       # a block of the neighbour's rows
+                    rp2, c2, v2 = wl.cfg5_rows(nb * wk["rows"], 4096, n=wk["n"], kmax=min(2048, wk["n"] // 2)) \
+                        if args.workload == "cfg5_spmm" else (None, None, None)
+                    views = [("NCCL-gathered Y", Yfull)]
+                    fview = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
+                    lib.spx_memcpy_d2d(fview.data_ptr(), fbuf, wk["m"] * C * 4, stream)
+                    views.append(("fused-exchange Y", fview))
+                    torch.cuda.synchronize()
+                    for name, buf in views:
+                        check_rows_against_oracle(buf[rows_lo + pick_dev], picked, name + ", own rows")
+                        if rp2 is not None:
+                            far = sample_rows(rp2, 3, 9)
+                            _, _, want = oracle_rows_spmm((rp2, c2, v2), far, wk["n"], wk["X"], None)
+                            got = buf[nb * wk["rows"] + torch.from_numpy(far).to(dev)].cpu().numpy()
+                            checks.append((name + ", a neighbour's rows", len(far), bits_equal(got, want)))
         else:
             dx = torch.from_numpy(wk["x"]).to(dev)
             dy = torch.empty(wk["rows"], device=dev, dtype=torch.float32)
-            working_set = 8 * ell.nnz_total + 4 * wk["n"]
-            ncopies = rotation_copies(working_set, world)
+            config, ncopies, need_flush = config_of(args, wk, world, ell.nnz_total)
             ells = [ell] + [lib.ell_create_csr(wk["rows"], wk["n"], rowptr, col, val) for _ in range(ncopies - 1)]
             dxs = [dx] + [dx.clone() for _ in range(ncopies - 1)]
             dys = [dy] + [torch.empty_like(dy) for _ in range(ncopies - 1)]
@@ -565,6 +727,22 @@ def measure(args, c):
 
             def e2e_step():
                 lib.spx_spmv_host(ell.h, hx.data_ptr(), 0 if hB is None else hB.data_ptr(), hy.data_ptr())
+
+            def run_checks():
+                """Sampled rows against the oracle's SpMV, within 1e-5 * (sum |w||x| + |bias|) per element
+                (the summation order differs from the reference's)."""
+                if args.no_check:
+                    return
+                torch.cuda.synchronize()
+                picked = sample_rows(rowptr)
+                E, orc, _ = oracle_rows_spmm(wk["csr"], picked, wk["n"], wk["x"][:, None], wk["bias"])
+                bsub = None if wk["bias"] is None else wk["bias"][picked]
+                want, bound = orc.spmv(E, wk["x"], bsub), orc.absbound(E, wk["x"], bsub)
+                outs = [("device-resident y", dys[rot[0]].cpu().numpy())]
+                if not args.no_e2e:
+                    outs.append(("host-buffer y", hy.numpy()))
+                for name, y in outs:
+                    checks.append((name, len(picked), bool((np.abs(y[picked] - want) <= 1e-5 * bound + 1e-30).all())))
         kernel_name = "spmm" if kind == "spmm" else "spmv"
     elif kind == "mlp":
         import tempfile
@@ -599,9 +777,31 @@ def measure(args, c):
         hX = torch.from_numpy(xl).pin_memory()
         h2d, d2h = hX.numel() * 4, model.out_features * Bl * 4
 
+        e2e_out = [None]
+
         def e2e_step():
-            model.run(hX.numpy().reshape(Bl, -1))
-        working_set = 64 << 20
+            e2e_out[0] = model.run(hX.numpy().reshape(Bl, -1))
+
+        def run_checks():
+            """The whole forward pass against the oracle's layer loop on this rank's batch columns:
+            identical chains up to the last layer, whose sigmoid may differ by a few ulp."""
+            if args.no_check:
+                return
+            import oracle
+            orc = oracle.Oracle()
+            cols = min(Bl, 16)                      # the oracle is scalar C: a few batch columns suffice
+            a = np.ascontiguousarray(xl[:, :cols])
+            for W_, b_, act in zip(wk["weights"], wk["biases"], wk["acts"]):
+                code = {"Relu": 1, "Sigmoid": 2, "Tanh": 3, None: 0}[act]
+                a = orc.spmm(orc.encode(W_), a, b_, act=code)
+            torch.cuda.synchronize()
+            got = np.empty((model.out_features, Bl), np.float32)
+            lib.spx_memcpy_d2h(got.ctypes.data_as(ctypes.c_void_p), model.device_output_ptr(), got.nbytes, stream)
+            torch.cuda.synchronize()
+            checks.append(("device-resident output", cols, bool(np.abs(got[:, :cols] - a).max() <= 1e-6)))
+            if e2e_out[0] is not None:
+                y = np.asarray(e2e_out[0]).ravel().reshape(model.out_features, Bl)
+                checks.append(("host-buffer output", cols, bool(np.abs(y[:, :cols] - a).max() <= 1e-6)))
         kernel_name = "spmm"
     elif kind == "convstack":
         import tempfile
@@ -630,7 +830,6 @@ def measure(args, c):
 
         def e2e_step():
             model.run(hX.numpy().reshape(Bl, Cc, H, W))
-        working_set = 64 << 20
         kernel_name = "conv"
     elif kind == "conv":
         B, Cc, H, W = wk["B"], wk["C"], wk["H"], wk["W"]
@@ -660,12 +859,28 @@ def measure(args, c):
             ell.conv2d(g, layout, dX.data_ptr(), Bl, dB.data_ptr(), sx.ACT_RELU, dY.data_ptr(), stream)
             hY.copy_(dY, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-        working_set = (dX.numel() + dY.numel()) * 4
+
+        def run_checks():
+            """Six output channels on up to four images against the oracle, bit for bit."""
+            if args.no_check:
+                return
+            import oracle
+            orc = oracle.Oracle()
+            torch.cuda.synchronize()
+            got = dY.cpu().numpy()
+            got_pf = got if not args.nchw else got.transpose(1, 2, 3, 0)
+            rows = sorted(set(int(v) for v in np.linspace(0, Cc - 1, 6)))
+            nb = min(Bl, 4)
+            sub = oracle.EllArrays(len(rows), Eh.n, Eh.r, Eh.Wd[rows], Eh.idx[rows], Eh.nnz[rows])
+            gd = dict(Cin=Cc, kH=3, kW=3, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+            x_pf = np.ascontiguousarray(xs[:nb].transpose(1, 2, 3, 0))
+            want = orc.conv2d(sub, gd, 0, x_pf, nb, wk["biases"][0][rows], 1)
+            checks.append(("device-resident output", len(rows) * nb, bits_equal(got_pf[rows][..., :nb], want)))
         kernel_name = "conv"
 
     job_bytes, job_flops = job_bytes_flops(wk, nnz_total)
-    rotating = kind in ("spmm", "spmv") and ncopies > 1
-    need_flush = working_set < (256 << 20) and not rotating
+    if kind not in ("spmm", "spmv"):
+        config, ncopies, need_flush = config_of(args, wk, world, 0)
     if need_flush:
         flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
@@ -734,13 +949,16 @@ def measure(args, c):
         e2e = {"value": to_value(wk, job_bytes, e2e_sec), "unit": metric_of(wk, args)[1], "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
                "timing": "host wall clock around synchronous host-buffer calls, max over ranks"}
+        if e2e_phases is not None:
+            e2e["phases_ms_rank0"] = {k: round(float(v), 4) for k, v in zip(("h2d_own_rows_of_X", "allgather_X_nvlink", "spmm", "d2h_own_rows_of_Y"), e2e_phases)}
+            e2e["path"] = "spx_spmm_host_sharded: 256-column panels pipelined over four streams; stage times overlap"
 
     ag = None
     if ag_step is not None:
         ag_total = timed(ag_step, max(3, min(args.steps, 10)), 2, False)
         ag_sec = ag_total / max(3, min(args.steps, 10))
         ag = {"ms_per_step": ag_sec * 1e3, "value": to_value(wk, job_bytes, ag_sec),
-              "note": "SpMM + NCCL all-gather of Y into every rank's full buffer"}
+              "note": "SpMM + in-place NCCL all-gather of Y into every rank's full buffer (spx_allgather_rows)"}
 
     fused = None
     if fused_step is not None:
@@ -749,10 +967,25 @@ def measure(args, c):
         fused = {"ms_per_step": f_sec * 1e3, "value": to_value(wk, job_bytes, f_sec),
                  "note": "SpMM whose epilogue stores Y into every rank's full buffer over NVLink (peer stores) + barrier"}
 
+    check = None
+    if run_checks is not None and not args.no_check:
+        run_checks()
+        ok_all = torch.tensor([1.0 if all(c[2] for c in checks) else 0.0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+        passed = bool(ok_all.item() == 1.0)
+        exact = kind in ("spmm", "conv")
+        check = {"rows": int(sum(c[1] for c in checks)), "bit_exact" if exact else "within_tolerance": passed,
+                 "against": "CPU oracle (oracle/ellpack_oracle.c) on sampled rows of every result buffer, all ranks",
+                 "buffers": [c[0] for c in checks], "failed": [c[0] for c in checks if not c[2]]}
+        if not exact:
+            check["tolerance"] = "1e-5 * (sum|w||x| + |bias|) per element" if kind == "spmv" else "1e-6 absolute on sigmoid outputs (chains before it are bit-identical)"
+
     # Measured denominator for the SpMM operand path: random 512-byte gathers from an L2-resident
-    # buffer, L1 bypassed (spx_probe_l2_gather), timed here on this GPU right after the workload.
+    # buffer, L1 bypassed (the bench-side probe library), timed here on this GPU right after the workload.
     l2_gather_tbps = None
-    if rank == 0 and kind in ("spmm", "mlp"):
+    probe = load_probe() if rank == 0 and kind in ("spmm", "mlp") else None
+    if probe is not None:
         probe_buf = torch.empty(32 << 20, dtype=torch.uint8, device=dev)
         probe_buf.zero_()
         sink = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -762,12 +995,13 @@ def measure(args, c):
         for i in range(5):                              # first pass warms L2; best of the rest
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            lib.spx_probe_l2_gather(probe_buf.data_ptr(), 32 << 20, 200, sink.data_ptr(), stream_ptr, ctypes.byref(nbytes))
+            if probe(probe_buf.data_ptr(), 32 << 20, 200, sink.data_ptr(), stream_ptr, ctypes.byref(nbytes)) != 0:
+                break
             e1.record()
             torch.cuda.synchronize()
             if i:
                 best = max(best, nbytes.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
-        l2_gather_tbps = best
+        l2_gather_tbps = best or None
         del probe_buf
 
     if rank == 0:
@@ -780,19 +1014,14 @@ def measure(args, c):
             "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "desc": wk["desc"],
-                       "l2": (f"{ncopies} rotating copies of the operands ({ncopies * working_set >> 20} MiB > L2), launches back to back"
-                              if rotating else "flushed between timed iterations (512 MiB write)" if need_flush
-                              else "inputs larger than L2"),
-                       "sharding": "rows of E split over ranks, X replicated, Y row-sharded" if kind in ("spmm", "spmv")
-                       else ("row-sharded layers + all-gather" if args.tp else "batch-sharded, no collective")},
+            "config": config,
             "gflops": job_flops / sec / 1e9,
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"of {peak_kind}", "kernel": kernel_name,
                          "algorithmic_bytes_per_launch": per_gpu_bytes / max(1, launches_per_step) if kind != "mlp" else None,
-                         "traffic": recorded_traffic(kernel_name, args.workload)},
+                         "traffic": recorded_traffic(kernel_name, args, world)},
         }
         # SpMM and conv move one 4-byte operand per FMA through the L2 -> SM gather path / shared
         # memory; that path, not HBM, is what their time tracks, so it is reported too.
@@ -807,8 +1036,10 @@ def measure(args, c):
                 line["roofline"]["operand_path"].update({
                     "l2_gather_peak_tbps": l2_gather_tbps,
                     "frac_of_l2_gather_peak": op_bytes / sec / 1e12 / l2_gather_tbps,
-                    "peak_source": "spx_probe_l2_gather on this GPU: random 512-byte gathers from a 32 MiB buffer, "
+                    "peak_source": "bench_l2_gather_probe on this GPU: random 512-byte gathers from a 32 MiB buffer, "
                                    "L1 bypassed; operands served by L1 hits can lift the fraction above 1"})
+        if check is not None:
+            line["check"] = check
         if e2e:
             line["e2e"] = e2e
         if ag:
@@ -817,8 +1048,8 @@ def measure(args, c):
             line["with_fused_allgather"] = fused
         if not args.no_cpu and world == 1:
             try:
-                run, frac, ckind, sample = cpu_sample_runner(args, wk)
-                med, reps = time_cpu(run, 5, warmup=1, budget_s=20.0)
+                run, frac, ckind, sample = cpu_sample_runner(args, wk, fraction=0.25 if args.workload == "cfg5_spmm" else None)
+                med, reps, _ = time_cpu(run, 5, warmup=1, budget_s=20.0)
                 csec = med / frac
                 line["cpu_baseline"] = {"value": to_value(wk, job_bytes, csec), "unit": unit, "cores": host_cores(), "kind": ckind,
                                         "sample": sample + f"; median of {reps} runs of {med * 1e3:.2f} ms, scaled by 1/{frac:.4f}",
@@ -833,35 +1064,57 @@ ALSO = [("cfg1_spmm", {}, "cfg1_spmm"), ("cfg1_spmv", {}, "cfg1_spmv"),
         ("cfg2_spmv", {"size": 16384, "sparsity": 0.90}, "cfg2_spmv_16384_s90"),
         ("cfg2_spmv", {"size": 65536, "sparsity": 0.90}, "cfg2_spmv_65536_s90"),
         ("cfg3_mlp", {}, "cfg3_mlp"), ("cfg4_conv", {}, "cfg4_conv")]
+# At N > 1 the second half of the metric rides along: the sparse MLP batch-sharded (no collective)
+# and row-sharded (an exchange after every layer), device-resident and through host buffers.
+ALSO_MULTI = [("cfg3_mlp", {"tp": False}, "cfg3_mlp_batch_sharded"), ("cfg3_mlp", {"tp": True}, "cfg3_mlp_row_sharded")]
+
+
+def also_entry(l2):
+    e = {"desc": l2["config"]["desc"], "sharding": l2["config"]["sharding"], "metric": l2["metric"], "value": l2["value"],
+         "unit": l2["unit"], "n_gpus": l2["n_gpus"], "ms_per_step": l2["ms_per_step"], "gflops": l2["gflops"],
+         "hbm_frac": l2["roofline"]["frac"], "l2": l2["config"]["l2"], "gpu_launches": l2["gpu_launches"]}
+    for k in ("check", "cpu_baseline"):
+        if k in l2:
+            e[k] = l2[k]
+    if "e2e" in l2:
+        e["e2e"] = {k: l2["e2e"][k] for k in ("value", "unit", "ms_per_step", "h2d_bytes_per_step", "d2h_bytes_per_step")}
+    return e
 
 
 def run_ours(args):
     c = setup_ours(args)
     line = measure(args, c)
     # The metric names SpMM, SpMV and the sparse MLP; the headline line carries the largest SpMM
-    # configuration, the other configurations ride along in "also" (device-resident timing only).
-    if c.rank == 0 and c.world == 1 and not args.no_also and args.workload == "cfg5_spmm" and args.scale == 1.0 \
-            and not args.rows and not args.cols:
+    # configuration, the other configurations ride along in "also".
+    default_run = not args.no_also and args.workload == "cfg5_spmm" and args.scale == 1.0 and not args.rows and not args.cols
+    if default_run:
         import copy
         also = {}
-        for name, over, label in ALSO:
+        for name, over, label in (ALSO if c.world == 1 else ALSO_MULTI):
             a2 = copy.copy(args)
-            a2.workload, a2.no_e2e, a2.no_cpu, a2.steps = name, True, True, max(args.steps, 20)
+            a2.workload, a2.steps = name, max(args.steps, 20)
+            a2.no_e2e = name != "cfg3_mlp"                    # host-buffer timing for the model only
+            a2.no_cpu = args.no_cpu
             for k, v in over.items():
                 setattr(a2, k, v)
             try:
-                l2 = measure(a2, c)
-                also[label] = {"desc": l2["config"]["desc"], "metric": l2["metric"], "value": l2["value"], "unit": l2["unit"],
-                              "ms_per_step": l2["ms_per_step"], "gflops": l2["gflops"],
-                              "hbm_frac": l2["roofline"]["frac"], "l2": l2["config"]["l2"]}
+                l2 = measure(a2, c)                           # collective: every rank takes part
+                if c.rank == 0:
+                    also[label] = also_entry(l2)
             except Exception as ex:
                 also[label] = {"error": repr(ex)}
-        line["also"] = also
+        if c.rank == 0:
+            line["also"] = also
+    failed = False
     if c.rank == 0:
         print(json.dumps(line), flush=True)
+        bad = [line.get("check")] + [v.get("check") for v in line.get("also", {}).values() if isinstance(v, dict)]
+        failed = any(ch is not None and not (ch.get("bit_exact", True) and ch.get("within_tolerance", True)) for ch in bad)
     if c.world > 1:
         c.dist.barrier()
         c.dist.destroy_process_group()
+    if failed:
+        raise SystemExit("bench.py: a result differs from the CPU oracle (see \"check\" in the line above)")
 
 
 def main():

@@ -10,8 +10,8 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Kernel
  *     entry points only enqueue work; they do not synchronise.
  *   - A handle may be used from several host threads for kernel launches, but entry points
- *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, its NCHW layout
- *     and batch sizes that are not a multiple of 4,
+ *     that grow per-handle scratch (spx_conv2d's first call per kernel shape, its NCHW and
+ *     F-major layouts and batch sizes that are not a multiple of 4,
  *     the first spx_spmv of a handle with n > 51200, the *_host calls) must not run concurrently
  *     on the same handle.
  *   - There is no CPU fallback: without a usable CUDA device every compute entry point
@@ -48,6 +48,9 @@ extern "C" {
 /* Activation tensor layouts of the convolution. */
 #define SPX_LAYOUT_PF     0   /* [C,H,W,B], batch fastest: conv2d_patchmajor_tiled, src/layers/conv_kernels.cpp:342 */
 #define SPX_LAYOUT_NCHW   1   /* [B,C,H,W]: conv2d_tiled_im2col_cmajor, src/layers/conv_kernels.cpp:233 */
+#define SPX_LAYOUT_FMAJOR 2   /* b + B*(c + C*(h + H*w)), i.e. [W,H,C,B]: the output of conv2d_tiled_im2col_fmajor
+                               * (src/layers/conv_kernels.cpp:150-230), input and output of conv2d_rbm_fmajor_implicit
+                               * (:66-147); same indexing as src/layers/pool.cpp:17-21 */
 
 /* Elementwise operators of spx_eltwise. */
 #define SPX_OP_RELU       1
@@ -96,14 +99,6 @@ int spx_event_create(void** event);
 int spx_event_destroy(void* event);
 int spx_event_record(void* event, void* stream);
 int spx_event_elapsed_ms(void* start, void* stop, float* ms);   /* synchronises on stop */
-
-/* Measurement aid, no counterpart in the reference: gathers 512-byte segments at pseudo-random
- * positions of buf (first power-of-two number of segments within `bytes`; choose a size that
- * fits L2), bypassing L1, `rounds` x 8 loads per lane on a full grid, and reports how many
- * bytes the launch reads.  bytes_read / device time = the L2 -> SM gather bandwidth that the
- * SpMM's operand traffic is compared with (bench.py).  sink: one writable float on the device. */
-int spx_probe_l2_gather(const void* buf, size_t bytes, uint32_t rounds, float* sink, void* stream,
-                        uint64_t* bytes_read);
 
 /* ---- CUDA graphs (the captured layer loop of SparseOnnxModel::run) ---------------------- */
 int spx_graph_capture_begin(void* stream);
@@ -168,7 +163,10 @@ int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float
  * to 32) must not exceed 1 048 576 slots, else SPX_ERR_LIMIT; the handle's device must be
  * current; all calls share the one array, so calls that overlap on the GPU race -- serialise
  * them; the first call on a device looks up the array's address and should come before any
- * stream capture.  Same arguments and results as spx_conv2d. */
+ * stream capture.  The CUDA runtime places the library's device code, and with it the 4 MiB
+ * array, on a GPU when the library is first used there: make one warm-up call per device (or any
+ * other call into this library) at start-up, before the host's own pool claims the remaining
+ * memory.  Same arguments and results as spx_conv2d. */
 int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                       const float* bias, int act, float* out, void* stream);
 /* out = op(a[, b]) elementwise; replaces applyRelu/Sigmoid/Tanh (src/layers/activation.cpp:3-62),
@@ -203,6 +201,22 @@ int spx_comm_destroy(spx_comm* c);
  * Y + g*rows_per_rank*ld of the full buffer.  (The reference has no multi-device path; this is
  * the exchange step of row-sharded SpMM, src/ellpack_matmul.cpp:26 being the row loop it splits.) */
 int spx_allgather_rows(spx_comm* c, float* Y, uint64_t rows_per_rank, uint64_t ld, void* stream);
+
+int spx_comm_info(const spx_comm* c, int* rank, int* world);      /* either pointer may be NULL */
+
+/* Row-sharded spx_spmm_host, one process per GPU: e holds this rank's rows of E (the split is the
+ * row loop of src/ellpack_matmul.cpp:26; the host-buffer call it replaces is the ellpack_matmul
+ * lambda of src/bindings.cpp:110-139).  X is the whole host operand (n x C, the same on every
+ * rank); each rank copies only rows [rank*ceil(n/world), ...) of it over PCIe, the ranks rebuild the
+ * replicated X on their devices with in-place all-gathers over NVLink, multiply, and copy their own
+ * rows of Y (m x C, m = this rank's rows) back to the host -- 256-column panels pipelined over four
+ * streams.  Collective: every rank of the communicator must make the call with the same n and C.
+ * phase_ms (may be NULL): four floats, the device time this rank spent in the copy in, the
+ * exchange, the multiply and the copy out, summed over the panels (the stages overlap, so their
+ * sum exceeds the call's duration).  comm == NULL or a world of 1: same as spx_spmm_host.
+ * Synchronous.  Up to 2048 columns. */
+int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* e, const float* X, uint32_t C, const float* bias,
+                          int act, float* Y, float* phase_ms);
 
 /* Stream-ordered barrier over the communicator (a one-float all-reduce): when it completes on this
  * rank's stream, every rank has finished the work it enqueued before its own call. */

@@ -135,13 +135,14 @@ class Oracle:
         return b
 
     def conv2d(self, E: EllArrays, geom: dict, layout: int, src, B: int, bias=None, act: int = 0):
-        """geom keys: Cin kH kW sH sW pH pW dH dW H W.  layout 0 = [C,H,W,B], 1 = NCHW."""
+        """geom keys: Cin kH kW sH sW pH pW dH dW H W.  layout 0 = [C,H,W,B], 1 = NCHW,
+        2 = F-major [W,H,C,B] (input and output)."""
         g = geom
         Ho = (g["H"] + 2 * g["pH"] - (g["dH"] * (g["kH"] - 1) + 1)) // g["sH"] + 1
         Wo = (g["W"] + 2 * g["pW"] - (g["dW"] * (g["kW"] - 1) + 1)) // g["sW"] + 1
         src = _f32(src)
         bias = _f32(bias)
-        shape = (E.m, Ho, Wo, B) if layout == 0 else (B, E.m, Ho, Wo)
+        shape = (E.m, Ho, Wo, B) if layout == 0 else (Wo, Ho, E.m, B) if layout == 2 else (B, E.m, Ho, Wo)
         dst = np.empty(shape, dtype=np.float32)
         self.lib.orc_conv2d(E.m, E.r, _fp(E.Wd), _up(E.idx), _up(E.nnz), g["Cin"], g["kH"], g["kW"],
                             g["sH"], g["sW"], g["pH"], g["pW"], g["dH"], g["dW"], g["H"], g["W"],
@@ -287,7 +288,9 @@ class Reference:
         Ho, Wo = C.c_uint32(), C.c_uint32()
         self.lib.ref_conv_out_dims(h, C.byref(Ho), C.byref(Wo))
         src = _f32(src)
-        shape = (Cout, Ho.value, Wo.value, B) if layout == 0 else (B, Cout, Ho.value, Wo.value)
+        # layouts 2 and 3 both write F-major [W,H,C,B]; 2 reads [C,H,W,B], 3 reads F-major
+        shape = (Cout, Ho.value, Wo.value, B) if layout == 0 else \
+            (Wo.value, Ho.value, Cout, B) if layout in (2, 3) else (B, Cout, Ho.value, Wo.value)
         dst = np.empty(shape, dtype=np.float32) if out is None else out
         self.lib.ref_conv_run(h, layout, _fp(src), B, _fp(dst))
         return dst

@@ -181,7 +181,12 @@ void orc_spmv_absbound(uint32_t m, uint32_t r, const float* Wd, const uint32_t* 
  * explicit im2col tile with zeros outside the image and hand it to
  * ellpack_matmul_fused, so per output element the arithmetic is the SpMM
  * chain over the row's nonzeros k = (cin, kh, kw) in storage order, with the
- * operand 0.0f for taps outside the image.  Geometry as in
+ * operand 0.0f for taps outside the image.  Layout 2 = F-major,
+ * b + B*(c + C*(h + H*w)) for input and output: the indexing of
+ * conv2d_rbm_fmajor_implicit (:66-147, off4_BCHW :8-11; it gathers on the fly,
+ * skips taps outside the image and walks each row's entries in ascending k,
+ * i.e. the same chain) and of the output of conv2d_tiled_im2col_fmajor
+ * (:150-230, whose input is read in the [C,H,W,B] order of patch_indices).  Geometry as in
  * src/sparse_onnx.cpp:411-451: begin pads only, ih = oh*stride + kh*dil - pad.
  * The reference's two tiled kernels mis-index stride_w > 1 (they advance the
  * input column by 1 per output column, :305-306 and :438-439); this
@@ -217,6 +222,8 @@ void orc_conv2d(uint32_t Cout, uint32_t r, const float* Wd, const uint32_t* idx,
                         if ((unsigned)ih < H && (unsigned)iw < W) {
                             size_t off = layout == 0
                                 ? (((size_t)cin * H + ih) * W + iw) * B + b
+                                : layout == 2
+                                ? (((size_t)iw * H + ih) * Cin + cin) * B + b
                                 : (((size_t)b * Cin + cin) * H + ih) * W + iw;
                             xv = src[off];
                         }
@@ -225,6 +232,8 @@ void orc_conv2d(uint32_t Cout, uint32_t r, const float* Wd, const uint32_t* idx,
                     y = orc_act(y, act);
                     size_t o = layout == 0
                         ? (((size_t)mo * Ho + oh) * Wo + ow) * B + b
+                        : layout == 2
+                        ? (((size_t)ow * Ho + oh) * Cout + mo) * B + b
                         : (((size_t)b * Cout + mo) * Ho + oh) * Wo + ow;
                     dst[o] = y;
                 }

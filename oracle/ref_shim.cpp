@@ -88,6 +88,21 @@ void* ref_conv_create(const float* weight, uint32_t Cout, uint32_t Cin, uint32_t
                 c.kmap.push_back(KMap{ ci, int32_t(kh * dH) - int32_t(pH), int32_t(kw * dW) - int32_t(pW) });
     if (bias) { rc->bias.assign(bias, bias + Cout); c.bias_ptr = rc->bias.data(); }
     c.fuse_relu = relu != 0;
+    // the tables the F-major kernels read, filled as the loader fills them
+    // (src/sparse_onnx.cpp:476-502): offsets of every (patch, k) in [C,H,W] order, one past the
+    // end for taps outside the image, and the row-block-merged plan
+    c.sentinel_off = size_t(Cin) * H * W;
+    c.patch_indices.resize(size_t(K) * c.H_out * c.W_out);
+    for (uint32_t ph = 0; ph < c.H_out; ++ph)
+        for (uint32_t pw = 0; pw < c.W_out; ++pw)
+            for (uint32_t k = 0; k < K; ++k) {
+                const int ih = int(ph) * int(sH) + c.kmap[k].dh, iw = int(pw) * int(sW) + c.kmap[k].dw;
+                const bool in = (unsigned)ih < H && (unsigned)iw < W;
+                c.patch_indices[(size_t(ph) * c.W_out + pw) * K + k] =
+                    in ? (size_t(c.kmap[k].cin) * H + size_t(ih)) * W + size_t(iw) : c.sentinel_off;
+            }
+    c.rbm = build_rbm_from_ellpack(c.E, c.bias_ptr, 8);
+    c.use_rbm = true;
     return rc;
 }
 void ref_conv_free(void* h) { delete static_cast<RefConv*>(h); }
@@ -97,11 +112,15 @@ void ref_conv_out_dims(void* h, uint32_t* Ho, uint32_t* Wo) {
 }
 void* ref_conv_ell(void* h) { return &static_cast<RefConv*>(h)->attr.E; }
 // layout 0: conv2d_patchmajor_tiled (src/layers/conv_kernels.cpp:342-470, [C,H,W,B]);
-// layout 1: conv2d_tiled_im2col_cmajor (:233-339, NCHW).
+// layout 1: conv2d_tiled_im2col_cmajor (:233-339, NCHW);
+// layout 2: conv2d_tiled_im2col_fmajor (:150-230, reads [C,H,W,B], writes F-major [W,H,C,B]);
+// layout 3: conv2d_rbm_fmajor_implicit (:66-147, F-major in and out).
 void ref_conv_run(void* h, int layout, const float* src, uint32_t B, float* dst) {
     auto* rc = static_cast<RefConv*>(h);
-    if (layout == 0) conv2d_patchmajor_tiled(rc->attr, src, B, dst);
-    else             conv2d_tiled_im2col_cmajor(rc->attr, src, B, dst);
+    if (layout == 0)      conv2d_patchmajor_tiled(rc->attr, src, B, dst);
+    else if (layout == 2) conv2d_tiled_im2col_fmajor(rc->attr, src, B, dst);
+    else if (layout == 3) conv2d_rbm_fmajor_implicit(rc->attr, src, B, dst);
+    else                  conv2d_tiled_im2col_cmajor(rc->attr, src, B, dst);
 }
 
 // ---- RBM plan (src/layers/rbm_conv.cpp:7-73) ----------------------------------------

@@ -28,7 +28,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
 
-def main():
+JSON_KEYS = ("M", "N", "C", "sparsity", "irregular", "nnz", "runs", "max_abs_diff_vs_cusparse", "ellpack_ms",
+             "cusparse_ms", "cublas_dense_ms", "gflops_ellpack", "speedup_vs_cusparse")
+
+
+def parse_args(argv=None):
+    """The flags of the reference's sparse_matmul_bench / sparse_matvec_bench
+    (benchmark-mkl/matmul/main_matmul.cpp:62-91) that have a meaning on the GPU."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=4096)
@@ -37,30 +43,42 @@ def main():
     ap.add_argument("--runs", type=int, default=50)
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--irregular", action="store_true")
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
+    if a.M < 1 or a.N < 1 or a.C < 1 or a.runs < 1 or not 0.0 <= a.sparsity <= 1.0:
+        ap.error("need M, N, C, runs >= 1 and 0 <= sparsity <= 1")
+    return a
 
+
+def build_case(a):
+    """Seeded host inputs of one run: CSR of the matrix, dense operand, bias (no GPU involved)."""
+    import workloads as wl
+    p = 1.0 - a.sparsity
+    if a.irregular:
+        kmax = max(1, min(a.N, int(32 * max(1.0, p * a.N))))
+        rowptr, col, val = wl.cfg5_rows(0, (a.M + 4095) // 4096 * 4096, n=a.N, kmax=kmax, mean=max(1.0, p * a.N), seed=a.seed)
+        rowptr = rowptr[:a.M + 1]
+        col, val = col[:int(rowptr[-1])], val[:int(rowptr[-1])]
+    else:
+        rowptr, col, val = wl.bernoulli_csr(a.seed, a.M, a.N, p)
+    rng = np.random.default_rng([a.seed, 1])
+    X = rng.uniform(-1, 1, (a.N, a.C)).astype(np.float32)
+    bias = rng.standard_normal(a.M).astype(np.float32)
+    return rowptr, col, val, X, bias
+
+
+def run(a):
+    """Times the three arms; returns (the JSON line as a dict, this library's result as a host array)."""
     import torch
 
     import spx_ctypes as sx
-    import workloads as wl
 
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     dev = torch.device("cuda", 0)
     lib = sx.Lib()
-    p = 1.0 - a.sparsity
-    if a.irregular:
-        kmax = max(1, min(a.N, int(32 * max(1.0, p * a.N))))
-        rowptr, col, val = wl.cfg5_rows(0, (a.M + 4095) // 4096 * 4096, n=a.N, kmax=kmax, mean=max(1.0, p * a.N), seed=a.seed)
-        rowptr, m = rowptr[:a.M + 1], a.M
-        col, val = col[:int(rowptr[-1])], val[:int(rowptr[-1])]
-    else:
-        rowptr, col, val = wl.bernoulli_csr(a.seed, a.M, a.N, p)
-        m = a.M
+    rowptr, col, val, X, bias = build_case(a)
+    m = a.M
     nnz = int(rowptr[-1])
-    rng = np.random.default_rng([a.seed, 1])
-    X = rng.uniform(-1, 1, (a.N, a.C)).astype(np.float32)
-    bias = rng.standard_normal(m).astype(np.float32)
 
     ell = lib.ell_create_csr(m, a.N, rowptr, col, val)
     dX, dB = torch.from_numpy(X).to(dev), torch.from_numpy(bias).to(dev)
@@ -100,6 +118,7 @@ def main():
     # agreement first (cuSPARSE sums in another order: tolerance, not bit equality)
     ours()
     torch.cuda.synchronize()
+    Y = dY.cpu().numpy().copy()
     ref = cusparse()
     ref = ref.reshape(m, -1)
     err = float((dY[:, :ref.shape[1]] - ref).abs().max())
@@ -108,6 +127,11 @@ def main():
            "cublas_dense_ms": median_ms(cublas) if dense is not None else None}
     out["gflops_ellpack"] = 2.0 * nnz * a.C / out["ellpack_ms"] / 1e6
     out["speedup_vs_cusparse"] = out["cusparse_ms"] / out["ellpack_ms"]
+    return out, Y
+
+
+def main(argv=None):
+    out, _ = run(parse_args(argv))
     print(json.dumps(out))
 
 

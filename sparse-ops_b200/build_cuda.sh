@@ -5,8 +5,11 @@
 set -e
 cd "$(dirname "$0")"
 NVCC=${NVCC:-nvcc}
-exec $NVCC -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -fmad=false \
+$NVCC -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -fmad=false \
     -Xcompiler -fPIC -shared -I../include -Icsrc/cuda \
     ${SPX_PTXAS_V:+-Xptxas -v} \
     -o libspx_b200.so csrc/cuda/abi.cu csrc/cuda/comm.cu csrc/cuda/spmm.cu csrc/cuda/spmv.cu \
-    csrc/cuda/conv.cu csrc/cuda/pool.cu csrc/cuda/eltwise.cu csrc/cuda/encode.cu csrc/cuda/probe.cu -ldl
+    csrc/cuda/conv.cu csrc/cuda/pool.cu csrc/cuda/eltwise.cu csrc/cuda/encode.cu -ldl
+# bench equipment, not part of the product library: the L2 -> SM gather bandwidth probe bench.py loads
+$NVCC -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -shared \
+    -o libspx_bench_probe.so csrc/bench/l2_gather_probe.cu

@@ -42,7 +42,9 @@ int sm_count(int device)
     return cache[device];
 }
 
-int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out)
+// The zero fill of the slabs is enqueued on `s`, the stream the caller fills them on afterwards:
+// a non-blocking stream is not ordered behind work on the default stream.
+int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out, cudaStream_t s)
 {
     spx_ell* e = new (std::nothrow) spx_ell();
     if (!e) return fail(SPX_ERR_OOM, "out of host memory");
@@ -61,11 +63,11 @@ int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out)
         err = cudaMalloc(&e->Wd, slots * sizeof(float));
         if (err == cudaSuccess) err = cudaMalloc(&e->idx, slots * sizeof(uint32_t));
         // padding slots hold Wd = 0.0f, idx = 0 like the reference's (src/ellpack_encoder.cpp:25)
-        if (err == cudaSuccess) err = cudaMemset(e->Wd, 0, slots * sizeof(float));
-        if (err == cudaSuccess) err = cudaMemset(e->idx, 0, slots * sizeof(uint32_t));
+        if (err == cudaSuccess) err = cudaMemsetAsync(e->Wd, 0, slots * sizeof(float), s);
+        if (err == cudaSuccess) err = cudaMemsetAsync(e->idx, 0, slots * sizeof(uint32_t), s);
     }
     if (err == cudaSuccess && m) err = cudaMalloc(&e->nnz, (size_t)m * sizeof(uint32_t));
-    if (err == cudaSuccess && m) err = cudaMemset(e->nnz, 0, (size_t)m * sizeof(uint32_t));
+    if (err == cudaSuccess && m) err = cudaMemsetAsync(e->nnz, 0, (size_t)m * sizeof(uint32_t), s);
     if (err != cudaSuccess) {
         cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz);
         delete e;
@@ -86,7 +88,11 @@ int set_row_order(spx_ell* e, const uint32_t* host_nnz)
     std::vector<uint32_t> order(e->m);
     for (uint32_t i = 0; i < e->m; ++i) order[start[e->r - host_nnz[i]]++] = i;
     e->long_rows = 0;
-    for (uint32_t i = 0; i < e->m; ++i) e->long_rows += host_nnz[i] >= 512 ? 1u : 0u;
+    e->min_nnz = host_nnz[0];
+    for (uint32_t i = 0; i < e->m; ++i) {
+        e->long_rows += host_nnz[i] >= 512 ? 1u : 0u;
+        e->min_nnz = std::min(e->min_nnz, host_nnz[i]);
+    }
     if (!e->row_order) SPX_CUDA(cudaMalloc(&e->row_order, (size_t)e->m * sizeof(uint32_t)));
     SPX_CUDA(cudaMemcpy(e->row_order, order.data(), (size_t)e->m * sizeof(uint32_t), cudaMemcpyHostToDevice));
     return SPX_OK;
@@ -101,6 +107,17 @@ static int ensure_stage(spx_ell* e, size_t bytes)
     e->stage_dev_bytes = 0;
     SPX_CUDA(cudaMalloc(&e->stage_dev, bytes));
     e->stage_dev_bytes = bytes;
+    return SPX_OK;
+}
+
+// Kernel entry points launch on the current device: a handle made on another GPU would hand the
+// kernel pointers it cannot reach, so that is refused on the host.
+int check_current_device(const spx_ell* e, const char* what)
+{
+    int cur = -1;
+    SPX_CUDA(cudaGetDevice(&cur));
+    if (cur != e->device)
+        return fail(SPX_ERR_ARG, "%s: the handle lives on device %d but device %d is current", what, e->device, cur);
     return SPX_OK;
 }
 
@@ -289,7 +306,7 @@ int spx_ell_create(uint32_t m, uint32_t n, uint32_t r, const float* Wd, const ui
         if (c > longest) longest = c;
     }
     spx_ell* e = nullptr;
-    int rc = alloc_ell(m, n, r, &e);
+    int rc = alloc_ell(m, n, r, &e, nullptr);
     if (rc != SPX_OK) return rc;
     e->nnz_total = total;
     e->max_nnz = longest;
@@ -334,7 +351,7 @@ int spx_ell_create_csr(uint32_t m, uint32_t n, const uint64_t* rowptr, const uin
                 return fail(SPX_ERR_ARG, "columns of row %u are not strictly ascending", i);
         }
     spx_ell* e = nullptr;
-    int rc = alloc_ell(m, n, r, &e);
+    int rc = alloc_ell(m, n, r, &e, nullptr);
     if (rc != SPX_OK) return rc;
     e->nnz_total = total;
     e->max_nnz = r;
@@ -377,8 +394,11 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
-    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch);
+    cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch); cudaFree(e->fm_scratch);
     for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : e->pipe_events) if (ev) cudaEventDestroy(ev);
+    if (e->aside_stream) cudaStreamDestroy(e->aside_stream);
+    for (cudaEvent_t ev : e->aside_ev) if (ev) cudaEventDestroy(ev);
     delete e;
     return SPX_OK;
 }
@@ -423,6 +443,7 @@ int spx_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const f
     if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
     if (!Y) return fail(SPX_ERR_ARG, "Y is null");
     if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    if (int rc = check_current_device(e, "spmm")) return rc;
     return launch_spmm(e, X, C, ldx, bias, act, Y, ldy, (cudaStream_t)stream);
 }
 
@@ -435,6 +456,7 @@ int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, c
     if (e->m == 0 || C == 0) return SPX_OK;
     if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
     if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    if (int rc = check_current_device(e, "spmm_bcast")) return rc;
     return launch_spmm_bcast(e, X, C, ldx, bias, act, Ys, nbuffers, row_offset, ldy, (cudaStream_t)stream);
 }
 
@@ -468,7 +490,8 @@ int spx_spmv(const spx_ell* e, const float* x, const float* bias, float* y, void
     if (!e) return fail(SPX_ERR_ARG, "handle is null");
     if (e->m == 0) return SPX_OK;
     if (!y) return fail(SPX_ERR_ARG, "y is null");
-    if (!x && e->nnz_total) return fail(SPX_ERR_ARG, "x is null");
+    if (!x && e->n) return fail(SPX_ERR_ARG, "x is null");   // the kernels stage all of x before any row
+    if (int rc = check_current_device(e, "spmv")) return rc;
     return launch_spmv(const_cast<spx_ell*>(e), x, bias, y, (cudaStream_t)stream);
 }
 
@@ -477,7 +500,8 @@ int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias
     if (!e) return fail(SPX_ERR_ARG, "handle is null");
     if (e->m == 0) return SPX_OK;
     if (!y) return fail(SPX_ERR_ARG, "y is null");
-    if (!x && e->nnz_total) return fail(SPX_ERR_ARG, "x is null");
+    if (!x && e->n) return fail(SPX_ERR_ARG, "x is null");
+    if (int rc = check_current_device(e, "spmv_reference_order")) return rc;
     return launch_spmv_reforder(e, x, bias, y, (cudaStream_t)stream);
 }
 
@@ -485,7 +509,8 @@ int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float
                const float* bias, int act, float* out, void* stream)
 {
     if (!e || !g) return fail(SPX_ERR_ARG, "handle / geometry is null");
-    if (layout != SPX_LAYOUT_PF && layout != SPX_LAYOUT_NCHW) return fail(SPX_ERR_ARG, "unknown layout %d", layout);
+    if (layout != SPX_LAYOUT_PF && layout != SPX_LAYOUT_NCHW && layout != SPX_LAYOUT_FMAJOR)
+        return fail(SPX_ERR_ARG, "unknown layout %d", layout);
     if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
     if (g->sH == 0 || g->sW == 0 || g->dH == 0 || g->dW == 0 || g->kH == 0 || g->kW == 0)
         return fail(SPX_ERR_ARG, "stride, dilation and kernel extent must be positive");
@@ -498,6 +523,7 @@ int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float
         return fail(SPX_ERR_ARG, "Ho / Wo inconsistent with the geometry");
     if (B == 0 || e->m == 0) return SPX_OK;
     if (!in || !out) return fail(SPX_ERR_ARG, "in / out is null");
+    if (int rc = check_current_device(e, "conv2d")) return rc;
     return launch_conv2d(const_cast<spx_ell*>(e), g, layout, in, B, bias, act, out, (cudaStream_t)stream);
 }
 
@@ -536,10 +562,10 @@ int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bi
     if (C >= 512 && C % 4 == 0 && (size_t)e->m * C * 4 >= ((size_t)64 << 20) && e->n) {
         for (cudaStream_t& st : e->pipe_streams)
             if (!st) SPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-        cudaStream_t s_in = e->pipe_streams[0], s_mm = e->pipe_streams[1], s_out = e->pipe_streams[2];
-        cudaEvent_t ev_in, ev_mm;
-        SPX_CUDA(cudaEventCreateWithFlags(&ev_in, cudaEventDisableTiming));
-        SPX_CUDA(cudaEventCreateWithFlags(&ev_mm, cudaEventDisableTiming));
+        cudaStream_t s_in = e->pipe_streams[0], s_mm = e->pipe_streams[2], s_out = e->pipe_streams[3];
+        for (int i = 0; i < 2; ++i)
+            if (!e->pipe_events[i]) SPX_CUDA(cudaEventCreate(&e->pipe_events[i]));
+        cudaEvent_t ev_in = e->pipe_events[0], ev_mm = e->pipe_events[1];
         cudaError_t err = cudaSuccess;
         if (bias) err = cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, s_in);
         for (uint32_t c0 = 0; c0 < C && err == cudaSuccess && rc == SPX_OK; c0 += 256) {
@@ -559,8 +585,6 @@ int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bi
         // on an error the earlier streams may still be busy: drain them before the staging is reused
         cudaStreamSynchronize(s_in);
         cudaStreamSynchronize(s_mm);
-        cudaEventDestroy(ev_in);
-        cudaEventDestroy(ev_mm);
         if (rc != SPX_OK) return rc;
         if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "spmm_host: pipelined copy failed: %s", cudaGetErrorString(err));
         return SPX_OK;
@@ -571,6 +595,95 @@ int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bi
     if (rc != SPX_OK) return rc;
     SPX_CUDA(cudaMemcpyAsync(Y, dY, (size_t)e->m * C * 4, cudaMemcpyDeviceToHost, nullptr));
     SPX_CUDA(cudaStreamSynchronize(nullptr));
+    return SPX_OK;
+}
+
+// Row-sharded SpMM on host buffers, one process per GPU.  Every rank holds the same host X but
+// copies only its own block of X's rows over PCIe; the ranks rebuild the replicated X on the
+// devices with in-place all-gathers over NVLink, multiply their rows of E and copy their own rows
+// of Y back.  The device copy of X is kept panel-major -- panel p is a contiguous
+// [rows_per_rank * world x width] matrix -- so that a rank's block of a panel is one contiguous
+// slab (what the all-gather wants) and the multiply of panel p can start while panel p+1 is still
+// on its way: four streams (copy in, exchange, multiply, copy out) chained by events per panel.
+int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* ce, const float* X, uint32_t C, const float* bias, int act,
+                          float* Y, float* phase_ms)
+{
+    spx_ell* e = const_cast<spx_ell*>(ce);
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    int rank = 0, world = 1;
+    if (comm) { int rc = spx_comm_info(comm, &rank, &world); if (rc != SPX_OK) return rc; }
+    if (phase_ms) phase_ms[0] = phase_ms[1] = phase_ms[2] = phase_ms[3] = 0.0f;
+    if (!comm || world == 1) return spx_spmm_host(ce, X, C, bias, act, Y);
+    if (C == 0) return SPX_OK;                       // nothing to exchange either: every rank returns here
+    if ((!Y && e->m) || (!X && e->n)) return fail(SPX_ERR_ARG, "X / Y is null");
+    DeviceGuard g(e->device);
+    constexpr uint32_t kPanel = 256;
+    const uint32_t panels = (C + kPanel - 1) / kPanel;
+    constexpr uint32_t kMaxPanels = sizeof(e->pipe_events) / sizeof(e->pipe_events[0]) / 8;    // 2 events x 4 stages each
+    if (panels > kMaxPanels) return fail(SPX_ERR_LIMIT, "spmm_host_sharded: C beyond %u columns", kMaxPanels * kPanel);
+    const uint64_t per = ((uint64_t)e->n + world - 1) / world;       // rows of X per rank (last block may be short)
+    const uint64_t lo = std::min<uint64_t>(e->n, per * rank), hi = std::min<uint64_t>(e->n, lo + per);
+    const size_t xb = round_up<size_t>((size_t)per * world * C * 4, 256);
+    const size_t bb = round_up<size_t>((size_t)e->m * 4 + 4, 256);
+    const size_t yb = round_up<size_t>((size_t)e->m * C * 4 + 4, 256);
+    int rc = ensure_stage(e, xb + bb + yb);
+    if (rc != SPX_OK) return rc;
+    char* base = static_cast<char*>(e->stage_dev);
+    float* dX = reinterpret_cast<float*>(base);
+    float* dB = reinterpret_cast<float*>(base + xb);
+    float* dY = reinterpret_cast<float*>(base + xb + bb);
+    for (cudaStream_t& st : e->pipe_streams)
+        if (!st) SPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    for (uint32_t i = 0; i < panels * 8; ++i)
+        if (!e->pipe_events[i]) SPX_CUDA(cudaEventCreate(&e->pipe_events[i]));
+    cudaStream_t st[4] = {e->pipe_streams[0], e->pipe_streams[1], e->pipe_streams[2], e->pipe_streams[3]};
+    auto ev = [&](uint32_t panel, int phase, int end) { return e->pipe_events[(panel * 4 + phase) * 2 + end]; };
+
+    cudaError_t err = cudaSuccess;
+    if (bias && e->m) err = cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, st[0]);
+    for (uint32_t p = 0; p < panels && err == cudaSuccess && rc == SPX_OK; ++p) {
+        const uint32_t c0 = p * kPanel, w = std::min<uint32_t>(kPanel, C - c0);
+        float* dXp = dX + (size_t)per * world * c0;                   // panel p: [per * world x w], contiguous
+        // 0: this rank's rows of the panel, host -> device
+        err = cudaEventRecord(ev(p, 0, 0), st[0]);
+        if (err == cudaSuccess && hi > lo)
+            err = cudaMemcpy2DAsync(dXp + lo * w, (size_t)w * 4, X + lo * C + c0, (size_t)C * 4, (size_t)w * 4, hi - lo,
+                                    cudaMemcpyHostToDevice, st[0]);
+        if (err == cudaSuccess) err = cudaEventRecord(ev(p, 0, 1), st[0]);
+        // 1: all ranks' rows of the panel, over NVLink
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(st[1], ev(p, 0, 1), 0);
+        if (err == cudaSuccess) err = cudaEventRecord(ev(p, 1, 0), st[1]);
+        if (err != cudaSuccess) break;
+        rc = spx_allgather_rows(comm, dXp, per, w, st[1]);
+        if (rc != SPX_OK) break;
+        err = cudaEventRecord(ev(p, 1, 1), st[1]);
+        // 2: multiply
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(st[2], ev(p, 1, 1), 0);
+        if (err == cudaSuccess) err = cudaEventRecord(ev(p, 2, 0), st[2]);
+        if (err != cudaSuccess) break;
+        if (e->m) rc = spx_spmm(e, dXp, w, w, bias ? dB : nullptr, act, dY + c0, C, st[2]);
+        if (rc != SPX_OK) break;
+        err = cudaEventRecord(ev(p, 2, 1), st[2]);
+        // 3: this rank's rows of Y, device -> host
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(st[3], ev(p, 2, 1), 0);
+        if (err == cudaSuccess) err = cudaEventRecord(ev(p, 3, 0), st[3]);
+        if (err == cudaSuccess && e->m)
+            err = cudaMemcpy2DAsync(Y + c0, (size_t)C * 4, dY + c0, (size_t)C * 4, (size_t)w * 4, e->m, cudaMemcpyDeviceToHost, st[3]);
+        if (err == cudaSuccess) err = cudaEventRecord(ev(p, 3, 1), st[3]);
+    }
+    // drain every stream (also after an error: the staging is reused by the next call)
+    for (int i = 3; i >= 0; --i) {
+        cudaError_t e2 = cudaStreamSynchronize(st[i]);
+        if (err == cudaSuccess) err = e2;
+    }
+    if (rc != SPX_OK) return rc;
+    if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "spmm_host_sharded: %s", cudaGetErrorString(err));
+    if (phase_ms)
+        for (uint32_t p = 0; p < panels; ++p)
+            for (int ph = 0; ph < 4; ++ph) {
+                float ms = 0.0f;
+                if (cudaEventElapsedTime(&ms, ev(p, ph, 0), ev(p, ph, 1)) == cudaSuccess) phase_ms[ph] += ms;
+            }
     return SPX_OK;
 }
 

@@ -107,6 +107,14 @@ int spx_comm_create(int rank, int world, const char id[SPX_UNIQUE_ID_BYTES], spx
     return SPX_OK;
 }
 
+int spx_comm_info(const spx_comm* c, int* rank, int* world)
+{
+    if (!c) return spx::fail(SPX_ERR_ARG, "communicator is null");
+    if (rank) *rank = c->rank;
+    if (world) *world = c->world;
+    return SPX_OK;
+}
+
 int spx_comm_barrier(spx_comm* c, void* stream)
 {
     if (!c || !c->comm) return spx::fail(SPX_ERR_ARG, "communicator is null");

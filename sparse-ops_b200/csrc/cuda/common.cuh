@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 
 #include "spx_b200.h"
 
@@ -19,6 +20,7 @@ struct spx_ell {
     uint32_t pitch = 0;          // row pitch in entries (0 when r == 0)
     uint64_t nnz_total = 0;
     uint32_t max_nnz = 0;        // longest row actually stored (<= r)
+    uint32_t min_nnz = 0;        // shortest row
     float* Wd = nullptr;         // m * pitch floats
     uint32_t* idx = nullptr;     // m * pitch column ids
     uint32_t* nnz = nullptr;     // m counts
@@ -47,14 +49,24 @@ struct spx_ell {
     // table, built on the first spx_spmv of such a handle.  spmv_win == UINT32_MAX: not applicable.
     uint32_t* spmv_split = nullptr;
     uint32_t spmv_win = 0;
+    // Second stream (highest priority) and the fork / join events of the SpMM that launches its
+    // long rows aside (spmm.cu), created on first use.
+    cudaStream_t aside_stream = nullptr;
+    cudaEvent_t aside_ev[2] = {nullptr, nullptr};
+    std::mutex aside_mu;
     // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
     void* stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
     // Scratch of the NCHW convolution path: the input and output in [C,H,W,B] order (conv.cu).
     void* conv_scratch = nullptr;
     size_t conv_scratch_bytes = 0;
-    // Streams of the pipelined host-buffer SpMM (copy in, multiply, copy out), created on first use.
-    cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
+    // Scratch of the F-major convolution path: input and output in [C,H,W,B] order (conv.cu).
+    void* fm_scratch = nullptr;
+    size_t fm_scratch_bytes = 0;
+    // Streams of the pipelined host-buffer SpMM (copy in, exchange, multiply, copy out) and the events
+    // that chain and time its stages, created on first use and kept.
+    cudaStream_t pipe_streams[4] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t pipe_events[64] = {};
 };
 
 namespace spx {
@@ -76,6 +88,16 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case SPX_ACT_TANH:    return tanhf(v);
     default:              return v;
     }
+}
+
+// (a0, a1) += w * (x0, x1) with ONE instruction: sm_100a's packed fma.rn.f32x2.  Each half is an
+// IEEE fused multiply-add rounded to nearest -- exactly fmaf -- so chains stay bit-identical while
+// the FMA instruction count halves.  The 64-bit pairs are formed inside the block, which leaves
+// the register allocator free to keep the operands in adjacent registers.
+__device__ __forceinline__ void fma_pair(float& a0, float& a1, float w, float x0, float x1) {
+    asm("{\n\t.reg .b64 pa, px, pw;\n\tmov.b64 pa, {%0, %1};\n\tmov.b64 px, {%3, %4};\n\tmov.b64 pw, {%2, %2};\n\t"
+        "fma.rn.f32x2 pa, pw, px, pa;\n\tmov.b64 {%0, %1}, pa;\n\t}"
+        : "+f"(a0), "+f"(a1) : "f"(w), "f"(x0), "f"(x1));
 }
 
 }  // namespace spx
@@ -113,7 +135,8 @@ int encode_device(const float* dW, uint32_t m, uint32_t n, cudaStream_t s, spx_e
 int decode_device(const spx_ell* e, float* dW, cudaStream_t s);
 int csr_to_ell_device(spx_ell* e, const uint64_t* d_rowptr, const uint32_t* d_col, const float* d_val,
                       cudaStream_t s);
-int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out);
+int alloc_ell(uint32_t m, uint32_t n, uint32_t r, spx_ell** out, cudaStream_t s);
+int check_current_device(const spx_ell* e, const char* what);
 // Builds e->row_order from host row counts (counting sort by length) and uploads it.
 int set_row_order(spx_ell* e, const uint32_t* host_nnz);
 }  // namespace spx

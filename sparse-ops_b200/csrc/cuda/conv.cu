@@ -63,6 +63,11 @@ conv_direct_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ ta
         const uint64_t px = col / p.B;
         ow = (uint32_t)(px % p.Wo);
         oh = (uint32_t)(px / p.Wo);
+    } else if (LAYOUT == SPX_LAYOUT_FMAJOR) {
+        b = (uint32_t)(col % p.B);
+        const uint64_t px = col / p.B;
+        oh = (uint32_t)(px % p.Ho);
+        ow = (uint32_t)(px / p.Ho);
     } else {
         ow = (uint32_t)(col % p.Wo);
         const uint64_t t = col / p.Wo;
@@ -84,6 +89,8 @@ conv_direct_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ ta
         if ((unsigned)ih < p.H && (unsigned)iw < p.W) {
             const size_t off = LAYOUT == SPX_LAYOUT_PF
                 ? (((size_t)cin * p.H + ih) * p.W + iw) * p.B + b
+                : LAYOUT == SPX_LAYOUT_FMAJOR
+                ? (((size_t)iw * p.H + ih) * p.Cin + cin) * p.B + b
                 : (((size_t)b * p.Cin + cin) * p.H + ih) * p.W + iw;
             xv = __ldg(in + off);
         }
@@ -92,6 +99,8 @@ conv_direct_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ ta
     acc = spx::apply_act(acc, act);
     const size_t o = LAYOUT == SPX_LAYOUT_PF
         ? (((size_t)mo * p.Ho + oh) * p.Wo + ow) * p.B + b
+        : LAYOUT == SPX_LAYOUT_FMAJOR
+        ? (((size_t)ow * p.Ho + oh) * p.Cout + mo) * p.B + b
         : (((size_t)b * p.Cout + mo) * p.Ho + oh) * p.Wo + ow;
     out[o] = acc;
 }
@@ -138,6 +147,24 @@ repitch_kernel(const float* __restrict__ src, uint32_t src_pitch, uint32_t src_c
     }
 }
 
+// dst[k][j][i][b] = src[i][j][k][b]: reverses the three outer dimensions (D0, D1, D2) of a tensor whose
+// innermost dimension B stays contiguous -- F-major [W,H,C,B] to [C,H,W,B] and back.
+__global__ void __launch_bounds__(256)
+reverse3_kernel(const float* __restrict__ src, uint32_t D0, uint32_t D1, uint32_t D2, uint32_t B,
+                float* __restrict__ dst)
+{
+    const uint64_t total = (uint64_t)D0 * D1 * D2 * B;
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t b = (uint32_t)(t % B);
+        uint64_t r = t / B;
+        const uint32_t i = (uint32_t)(r % D0);
+        r /= D0;
+        const uint32_t j = (uint32_t)(r % D1);
+        const uint32_t k = (uint32_t)(r / D1);
+        dst[t] = __ldg(src + ((((uint64_t)i * D1 + j) * D2 + k) * B + b));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // conv_pf_tile_kernel: the fast path for the [C,H,W,B] layout with B % 4 == 0.
 //
@@ -156,6 +183,9 @@ repitch_kernel(const float* __restrict__ src, uint32_t src_pitch, uint32_t src_c
 // of the FP32 peak; HBM / L2 traffic is the input patch once per CTA (16 or 32 output channels)
 // plus the output once.
 // ---------------------------------------------------------------------------------------------
+#ifndef SPX_CONV_FMA2
+#define SPX_CONV_FMA2 1         // packed fma.rn.f32x2 in the tiled kernels (same rounding per element)
+#endif
 constexpr int kTileH = 4, kTileW = 8, kTileWarps = 16;
 
 struct TileParams {
@@ -263,10 +293,15 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
                         const float4 xv = *reinterpret_cast<const float4*>(xs + off[g]);
+#if SPX_CONV_FMA2
+                        spx::fma_pair(acc[g].x, acc[g].y, wt, xv.x, xv.y);
+                        spx::fma_pair(acc[g].z, acc[g].w, wt, xv.z, xv.w);
+#else
                         acc[g].x = fmaf(wt, xv.x, acc[g].x);
                         acc[g].y = fmaf(wt, xv.y, acc[g].y);
                         acc[g].z = fmaf(wt, xv.z, acc[g].z);
                         acc[g].w = fmaf(wt, xv.w, acc[g].w);
+#endif
                     }
                 }
                 pos += cnt;
@@ -392,10 +427,15 @@ __device__ __forceinline__ void rbm_row(float4 (&acc)[kRbmRows][G], uint32_t hm,
         const float wt = __shfl_sync(0xffffffffu, wsrc, t);
 #pragma unroll
         for (int g = 0; g < G; ++g) {
+#if SPX_CONV_FMA2
+            spx::fma_pair(acc[R][g].x, acc[R][g].y, wt, x[g].x, x[g].y);
+            spx::fma_pair(acc[R][g].z, acc[R][g].w, wt, x[g].z, x[g].w);
+#else
             acc[R][g].x = fmaf(wt, x[g].x, acc[R][g].x);
             acc[R][g].y = fmaf(wt, x[g].y, acc[R][g].y);
             acc[R][g].z = fmaf(wt, x[g].z, acc[R][g].z);
             acc[R][g].w = fmaf(wt, x[g].w, acc[R][g].w);
+#endif
         }
     }
 }
@@ -783,7 +823,36 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     const uint32_t B4 = padded_batch(B);
     ConvParams p4 = p;
     p4.B = B4;
-    if (e->r && e->cols_ascending && pf_tile_covers(p4)) {
+    // F-major tensors, b + B*(c + C*(h + H*w)): [W,H,C,B] is [C,H,W,B] with the three outer
+    // dimensions reversed, so the tiled kernels are reached through two more streaming passes
+    // (reverse in, reverse out) in scratch of their own; shapes the tiled kernels do not cover
+    // gather straight from the F-major tensor in the general kernel below.
+    if (layout == SPX_LAYOUT_FMAJOR && e->r && e->cols_ascending && pf_tile_covers(p4)) {
+        const uint64_t n_in = (uint64_t)g->Cin * g->H * g->W * B, n_out = (uint64_t)g->Cout * g->Ho * g->Wo * B;
+        const uint64_t in_slab = (n_in + 63) / 64 * 64;
+        const size_t need = (size_t)(in_slab + n_out) * sizeof(float);
+        if (e->fm_scratch_bytes < need) {
+            if (e->fm_scratch) cudaFree(e->fm_scratch);
+            e->fm_scratch = nullptr;
+            e->fm_scratch_bytes = 0;
+            SPX_CUDA(cudaMalloc(&e->fm_scratch, need));
+            e->fm_scratch_bytes = need;
+        }
+        float* in_pf = static_cast<float*>(e->fm_scratch);
+        float* out_pf = in_pf + in_slab;
+        auto reverse3 = [&](const float* src, uint32_t D0, uint32_t D1, uint32_t D2, float* dst, uint64_t total) {
+            const unsigned blocks = (unsigned)std::min<uint64_t>((total + 255) / 256, (uint64_t)sm_count(e->device) * 32);
+            reverse3_kernel<<<blocks, 256, 0, s>>>(src, D0, D1, D2, B, dst);
+            SPX_LAUNCH_CHECK("reverse3_kernel");
+            return SPX_OK;
+        };
+        rc = reverse3(in, g->W, g->H, g->Cin, in_pf, n_in);                   // [W,H,C,B] -> [C,H,W,B]
+        if (rc != SPX_OK) return rc;
+        rc = launch_conv2d(e, g, SPX_LAYOUT_PF, in_pf, B, bias, act, out_pf, s);
+        if (rc != SPX_OK) return rc;
+        return reverse3(out_pf, g->Cout, g->Ho, g->Wo, out, n_out);           // [C,Ho,Wo,B] -> [Wo,Ho,C,B]
+    }
+    if (layout != SPX_LAYOUT_FMAJOR && e->r && e->cols_ascending && pf_tile_covers(p4)) {
         const bool nchw = layout == SPX_LAYOUT_NCHW && B > 1;
         const bool pad = B4 != B;
         if (!nchw && !pad) {
@@ -840,6 +909,8 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     dim3 grid((unsigned)gx, e->m);
     if (layout == SPX_LAYOUT_PF)
         conv_direct_kernel<SPX_LAYOUT_PF><<<grid, 256, 0, s>>>(e->Wd, e->taps, e->nnz, e->pitch, p, in, bias, act, out);
+    else if (layout == SPX_LAYOUT_FMAJOR)
+        conv_direct_kernel<SPX_LAYOUT_FMAJOR><<<grid, 256, 0, s>>>(e->Wd, e->taps, e->nnz, e->pitch, p, in, bias, act, out);
     else
         conv_direct_kernel<SPX_LAYOUT_NCHW><<<grid, 256, 0, s>>>(e->Wd, e->taps, e->nnz, e->pitch, p, in, bias, act, out);
     SPX_LAUNCH_CHECK("conv_direct_kernel");
@@ -922,15 +993,16 @@ extern "C" int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int l
     int rc = static_taps_address(cur, &taps);
     if (rc != SPX_OK) return rc;
 
+    // every limit is checked before the first launch: a refused call leaves the shared table alone
+    const uint64_t per_m = (uint64_t)g->Ho * g->Wo * B;
+    const uint64_t gx = (per_m + 255) / 256;
+    if (gx > 0x7fffffffull || e->m > 65535) return fail(SPX_ERR_LIMIT, "conv2d_static: output too large for one launch");
     cudaStream_t s = (cudaStream_t)stream;
     if (e->r) {
         build_taps_kernel<<<e->m, 128, 0, s>>>(e->idx, e->nnz, e->m, e->pitch, g->kH, g->kW, taps);
         SPX_LAUNCH_CHECK("build_taps_kernel");
     }
     ConvParams p{g->Cin, g->Cout, g->kH, g->kW, g->sH, g->sW, g->pH, g->pW, g->dH, g->dW, g->H, g->W, g->Ho, g->Wo, B};
-    const uint64_t per_m = (uint64_t)g->Ho * g->Wo * B;
-    const uint64_t gx = (per_m + 255) / 256;
-    if (gx > 0x7fffffffull || e->m > 65535) return fail(SPX_ERR_LIMIT, "conv2d_static: output too large for one launch");
     dim3 grid((unsigned)gx, e->m);
     if (layout == SPX_LAYOUT_PF)
         conv_direct_kernel<SPX_LAYOUT_PF><<<grid, 256, 0, s>>>(e->Wd, taps, e->nnz, e->pitch, p, in, bias, act, out);

@@ -110,7 +110,7 @@ int encode_device(const float* dW, uint32_t m, uint32_t n, cudaStream_t s, spx_e
         if (err != cudaSuccess) { cudaFree(d_nnz); return fail(SPX_ERR_CUDA, "encode: count pass failed: %s", cudaGetErrorString(err)); }
     }
     spx_ell* e = nullptr;
-    int rc = alloc_ell(m, n, r, &e);
+    int rc = alloc_ell(m, n, r, &e, s);      // zero fill on s, ahead of the pack below
     if (rc != SPX_OK) { cudaFree(d_nnz); return rc; }
     if (m) {
         cudaMemcpyAsync(e->nnz, d_nnz, (size_t)m * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s);

@@ -19,6 +19,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 
 namespace {
 
@@ -430,6 +431,68 @@ static BlockMap block_map(const spx_ell* e, uint32_t C, uint32_t panels, uint32_
     return bm;
 }
 
+// Whether the long rows should run as a launch of their own (see launch_spmm_bcast).  Estimates:
+// the kernel moves 4*C bytes of X per stored entry at about 17 TB/s; the longest row's chain takes
+// max_nnz / 4 round trips of about 1.2 us on the wide path.  SPX_SPMM_SPLIT=0|1 overrides.
+static bool split_long_rows(const spx_ell* e, uint32_t C)
+{
+    static const int forced = [] { const char* v = getenv("SPX_SPMM_SPLIT"); return v ? atoi(v) : -1; }();
+    if (e->long_rows == 0 || e->long_rows >= e->m || C <= 128) return false;
+    if (forced >= 0) return forced != 0;
+    const double kernel_us = (double)e->nnz_total * C * 4.0 / 17e6 * (148.0 / sm_count(e->device));
+    const double chain_us = e->max_nnz / 4.0 * 1.2;
+    return chain_us > 0.25 * kernel_us;
+}
+
+// Long rows on the handle's second stream, narrow panels; all other rows on `s`, wide panels.
+// Fork and join are events, so the pair also records into a stream capture as two parallel nodes.
+static int launch_long_rows_aside(const spx_ell* ce, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                                  const PeerOut& out, uint64_t ldy, cudaStream_t s)
+{
+    spx_ell* e = const_cast<spx_ell*>(ce);
+    std::lock_guard<std::mutex> lk(e->aside_mu);       // one fork / join at a time per handle
+    if (!e->aside_stream) {
+        int lo = 0, hi = 0;
+        if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&e->aside_stream, cudaStreamNonBlocking, hi) != cudaSuccess ||
+            cudaEventCreateWithFlags(&e->aside_ev[0], cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&e->aside_ev[1], cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return -1;
+        }
+    }
+    SPX_CUDA(cudaEventRecord(e->aside_ev[0], s));
+    SPX_CUDA(cudaStreamWaitEvent(e->aside_stream, e->aside_ev[0], 0));
+    {   // rows 0 .. long_rows-1 of the schedule
+        const uint32_t panels = (C + 127) / 128, rows = e->long_rows;
+        const uint32_t wpb = rows >= 8 ? 8 : rows >= 4 ? 4 : 2;
+        BlockMap bm{};
+        bm.row_blocks = (rows + wpb - 1) / wpb;
+        bm.panels = panels;
+        bm.head = bm.row_blocks;                         // panel-minor: every long row starts on all panels at once
+        bm.blocks = bm.row_blocks * panels;
+        spmm_gather_vec<1, 8, 4><<<bm.blocks, wpb * 32, 0, e->aside_stream>>>(e->Wd, e->idx, e->nnz, e->row_order, rows, e->pitch,
+                                                                            X, C, ldx, bias, act, out, ldy, bm);
+        SPX_LAUNCH_CHECK("spmm_gather_vec");
+    }
+    SPX_CUDA(cudaEventRecord(e->aside_ev[1], e->aside_stream));
+    {   // the remaining rows
+        const uint32_t panels = (C + 255) / 256, rows = e->m - e->long_rows;
+        uint32_t wpb = 8;
+        while (wpb > 2 && (uint64_t)((rows + wpb - 1) / wpb) * panels < (uint64_t)sm_count(e->device) * 8) wpb >>= 1;
+        BlockMap bm{};
+        bm.row_blocks = (rows + wpb - 1) / wpb;
+        bm.panels = panels;
+        bm.head = 0;
+        bm.blocks = bm.row_blocks * panels;
+        spmm_gather_vec<2, 4, 4><<<bm.blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order + e->long_rows, rows, e->pitch,
+                                                              X, C, ldx, bias, act, out, ldy, bm);
+        SPX_LAUNCH_CHECK("spmm_gather_vec");
+    }
+    SPX_CUDA(cudaStreamWaitEvent(s, e->aside_ev[1], 0));
+    return SPX_OK;
+}
+
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s)
 {
@@ -491,8 +554,14 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
         const int nv = gather_nv(e->n, C);
         // A row is one dependent chain of gathers, G rows of X per round trip to L2 (about a
         // microsecond under load).  When the longest row's chain is a large part of the whole
-        // kernel (few rows per GPU, skewed lengths) it becomes the tail: use narrower panels with
-        // more gathers in flight per row instead (same bytes in flight per SM, shorter chain).
+        // kernel (few rows per GPU, skewed lengths) it becomes the tail: the rows with 512 and
+        // more entries then go out as a launch of their own on a second stream, on 128-column
+        // panels with eight rows of X in flight per round trip (half the round trips), while the
+        // remaining rows run next to them on the caller's stream.
+        if (nv == 2 && split_long_rows(e, C)) {
+            int rc = launch_long_rows_aside(e, X, C, ldx, bias, act, out, ldy, s);
+            if (rc != -1) return rc;            // -1: the second stream could not be set up
+        }
         const uint32_t panels = (C + 128 * nv - 1) / (128 * nv);
         const uint32_t wpb = gather_wpb(e, panels);
         const BlockMap bm = block_map(e, C, panels, wpb);

@@ -13,6 +13,7 @@
 // (a multiple of the SM count) so x is staged once per CTA.
 #include "common.cuh"
 
+#include <algorithm>
 #include <climits>
 #include <cstdint>
 #include <cstdlib>
@@ -26,6 +27,12 @@ __device__ __forceinline__ float group_sum(float v) {
     return v;
 }
 
+// Small matrices are latency-bound: staging x, the row schedule, the row length and the slabs
+// would be four memory round trips in a row.  So the kernel is software-pipelined: a group asks
+// for its first row's id and length and for that row's first slab vectors BEFORE x is staged (none
+// of them depends on x), and while a row is summed the next row's id, length and first vectors
+// are already in flight.  row_order may be null (rows of near-equal length): slot == row then, and
+// one dependent load goes away.
 template <int LPR, bool SMEM>
 __global__ void __launch_bounds__(1024)
 spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
@@ -34,6 +41,41 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y)
 {
     extern __shared__ __align__(16) float xs[];
+    constexpr int UNR = 4;                       // 16-byte vectors of Wd and of idx in flight per lane
+    constexpr uint32_t STEP = LPR * 4 * UNR;     // entries a group consumes per chunk
+    const uint32_t lane = threadIdx.x & (LPR - 1);
+    const uint32_t groups_per_block = blockDim.x / LPR;
+    const uint32_t group = blockIdx.x * groups_per_block + threadIdx.x / LPR;
+    const uint32_t stride = gridDim.x * groups_per_block;
+    // All lanes of a warp run the same number of row iterations so that the shuffles below
+    // always see the full warp.
+    const uint32_t iters = (m + stride - 1) / stride;
+
+    float4 wv[UNR];
+    uint4 kv[UNR];
+    // entries >= nn are padding and are neither loaded nor multiplied
+    auto load_chunk = [&](uint32_t row, uint32_t nn, uint32_t j) {
+        const float4* __restrict__ w4 = reinterpret_cast<const float4*>(Wd + (size_t)row * pitch);
+        const uint4* __restrict__ k4 = reinterpret_cast<const uint4*>(idx + (size_t)row * pitch);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t ju = j + u * LPR * 4;
+            if (ju < nn) {
+                wv[u] = __ldcs(w4 + (ju >> 2));
+                kv[u] = __ldcs(k4 + (ju >> 2));
+            } else {
+                wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                kv[u] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+    // slots of the sorted row schedule are dealt round-robin: every group gets long and short rows
+    uint32_t slot = group;
+    bool live = slot < m;
+    uint32_t row = live ? (row_order ? __ldg(row_order + slot) : slot) : 0u;
+    uint32_t nn = live ? __ldg(nnz + row) : 0u;
+    load_chunk(row, nn, lane * 4);
+
     if (SMEM) {
         // n floats, 16-byte vectors where alignment allows
         const uint32_t n4 = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? (n >> 2) : 0;
@@ -44,40 +86,17 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     }
     const float* __restrict__ xsrc = SMEM ? xs : x;
 
-    const uint32_t lane = threadIdx.x & (LPR - 1);
-    const uint32_t groups_per_block = blockDim.x / LPR;
-    const uint32_t group = blockIdx.x * groups_per_block + threadIdx.x / LPR;
-    const uint32_t stride = gridDim.x * groups_per_block;
-    // All lanes of a warp run the same number of row iterations so that the shuffles below
-    // always see the full warp.
-    const uint32_t iters = (m + stride - 1) / stride;
-
     for (uint32_t it = 0; it < iters; ++it) {
-        // slots of the sorted row schedule are dealt round-robin: every group gets long and short rows
-        const uint32_t slot = group + it * stride;
-        const bool live = slot < m;
-        const uint32_t row = live ? __ldg(row_order + slot) : 0u;
-        const uint32_t nn = live ? __ldg(nnz + row) : 0u;
-        const float4* __restrict__ w4 = reinterpret_cast<const float4*>(Wd + (size_t)row * pitch);
-        const uint4* __restrict__ k4 = reinterpret_cast<const uint4*>(idx + (size_t)row * pitch);
+        // the next row's id and length travel while this row is summed
+        const uint32_t slot_n = slot + stride;
+        const bool live_n = (it + 1 < iters) && slot_n < m;
+        const uint32_t row_n = live_n ? (row_order ? __ldg(row_order + slot_n) : slot_n) : 0u;
+        const uint32_t nn_n = live_n ? __ldg(nnz + row_n) : 0u;
+        const float b = (live && bias) ? __ldg(bias + row) : 0.0f;
+
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        // UNR 16-byte vectors of Wd and of idx in flight per lane; entries >= nn are padding and
-        // are neither loaded nor multiplied
-        constexpr int UNR = 4;
-        for (uint32_t j = lane * 4; j < nn; j += LPR * 4 * UNR) {
-            float4 wv[UNR];
-            uint4 kv[UNR];
-#pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-                const uint32_t ju = j + u * LPR * 4;
-                if (ju < nn) {
-                    wv[u] = __ldcs(w4 + (ju >> 2));
-                    kv[u] = __ldcs(k4 + (ju >> 2));
-                } else {
-                    wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    kv[u] = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
+        for (uint32_t j = lane * 4; j < nn; j += STEP) {
+            if (j != lane * 4) load_chunk(row, nn, j);          // the first chunk is already here
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const uint32_t ju = j + u * LPR * 4;
@@ -87,9 +106,11 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 if (ju + 3 < nn) a3 = fmaf(wv[u].w, xsrc[kv[u].w], a3);
             }
         }
+        load_chunk(row_n, nn_n, lane * 4);                      // first vectors of the next row
         float acc = (a0 + a1) + (a2 + a3);
         acc = group_sum<LPR>(acc);
-        if (live && lane == 0) y[row] = (bias ? __ldg(bias + row) : 0.0f) + acc;
+        if (live && lane == 0) y[row] = b + acc;
+        slot = slot_n; live = live_n; row = row_n; nn = nn_n;
     }
 }
 
@@ -229,20 +250,6 @@ spmv_reforder_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ 
     if (live && l == 0) y[row] = (bias ? __ldg(bias + row) : 0.0f) + a;
 }
 
-template <int LPR, bool SMEM>
-int launch_one(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s,
-               int threads, int blocks, size_t smem)
-{
-    auto kfn = spmv_ell_kernel<LPR, SMEM>;
-    if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return spx::fail(SPX_ERR_CUDA, "spmv: shared memory opt-in failed: %s", cudaGetErrorString(err));
-    }
-    kfn<<<blocks, threads, smem, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->n, e->pitch, x, bias, y);
-    SPX_LAUNCH_CHECK("spmv_ell_kernel");
-    return SPX_OK;
-}
-
 // Shrinks a persistent grid so that every group runs the same number of row iterations
 // (a grid of 9324 groups over 16384 rows would give some groups two rows and others one).
 static int balanced_blocks(uint64_t rows, int groups_per_block, int max_blocks)
@@ -260,16 +267,42 @@ int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cu
     const size_t xbytes = (size_t)e->n * sizeof(float);
     const size_t kSmemMax = 200 * 1024;      // leaves room for a second small CTA's static needs
     const uint64_t groups_needed = e->m;
+    // Rows of near-equal length need no schedule: slot == row saves one dependent load per row.
+    const uint32_t* order = (e->max_nnz - e->min_nnz) * 8u <= e->max_nnz ? nullptr : e->row_order;
     if (xbytes <= kSmemMax) {
         // CTAs per SM limited by the staged copy of x; 2048 threads per SM at most.
         int per_sm = (int)((220 * 1024) / (xbytes + 1024));
         if (per_sm < 1) per_sm = 1;
         if (per_sm > 4) per_sm = 4;
-        int threads = 2048 / per_sm;
-        if (threads > 1024) threads = 1024;
-        threads &= ~31;
-        const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * per_sm);
-        return launch_one<LPR, true>(e, x, bias, y, s, threads, blocks, xbytes);
+        // Rows per group (iters) as if every SM held per_sm CTAs of full size; then the same number of
+        // CTAs on every SM -- as few as carry the rows in that many iterations (x is staged once per
+        // CTA) -- each with equally many groups.  A grid that is not a multiple of the SM count
+        // leaves some SMs with one CTA more than others for the whole kernel.
+        int threads_full = 2048 / per_sm;
+        if (threads_full > 1024) threads_full = 1024;
+        threads_full &= ~31;
+        const uint64_t cap = (uint64_t)sms * per_sm * (threads_full / LPR);
+        const uint64_t iters = (groups_needed + cap - 1) / cap;
+        const uint64_t per_iter = (groups_needed + iters - 1) / iters;         // groups that must exist
+        int threads = threads_full, blocks = sms * per_sm;
+        for (int k = 1; k <= per_sm; ++k) {
+            const uint64_t g = (per_iter + (uint64_t)sms * k - 1) / ((uint64_t)sms * k);
+            const uint64_t t = (g * LPR + 31) / 32 * 32;
+            const uint64_t tmax = std::min<uint64_t>(1024, 2048 / k);
+            if (t <= tmax) {
+                threads = (int)t;
+                blocks = (int)std::min<uint64_t>((uint64_t)sms * k, (per_iter + g - 1) / g);
+                break;
+            }
+        }
+        auto kfn = spmv_ell_kernel<LPR, true>;
+        if (xbytes > 48 * 1024) {
+            cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xbytes);
+            if (err != cudaSuccess) return spx::fail(SPX_ERR_CUDA, "spmv: shared memory opt-in failed: %s", cudaGetErrorString(err));
+        }
+        kfn<<<blocks, threads, xbytes, s>>>(e->Wd, e->idx, e->nnz, order, e->m, e->n, e->pitch, x, bias, y);
+        SPX_LAUNCH_CHECK("spmv_ell_kernel");
+        return SPX_OK;
     }
     if (e->spmv_split) {
         const int blocks = balanced_blocks(groups_needed, 1024 / LPR, sms);
@@ -284,7 +317,9 @@ int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cu
     }
     int threads = 512;
     const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * 4);
-    return launch_one<LPR, false>(e, x, bias, y, s, threads, blocks, 0);
+    spmv_ell_kernel<LPR, false><<<blocks, threads, 0, s>>>(e->Wd, e->idx, e->nnz, order, e->m, e->n, e->pitch, x, bias, y);
+    SPX_LAUNCH_CHECK("spmv_ell_kernel");
+    return SPX_OK;
 }
 
 }  // namespace

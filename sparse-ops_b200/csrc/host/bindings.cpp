@@ -83,7 +83,12 @@ PYBIND11_MODULE(sparseops_backend, m)
         .def_property_readonly("nnz_total", &Ellpack::nnz_total)
         .def("shard_rows", [](const Ellpack& E, uint32_t g, uint32_t G, bool upload) { return E.shard_rows(g, G, upload); },
              py::arg("index"), py::arg("count"), py::arg("upload") = true,
-             "Rows [index*ceil(m/count), ...) as an independent Ellpack (uploaded unless upload=False)");
+             "Rows [index*ceil(m/count), ...) as an independent Ellpack (uploaded unless upload=False)")
+        .def("shard_range", [](const Ellpack& E, uint32_t lo, uint32_t hi, bool upload) { return E.shard_range(lo, hi, upload); },
+             py::arg("lo"), py::arg("hi"), py::arg("upload") = true, "Rows [lo, hi) as an independent Ellpack")
+        .def("balanced_row_split", [](const Ellpack& E, uint32_t G, uint32_t row_cost) { return E.balanced_row_split(G, row_cost); },
+             py::arg("count"), py::arg("row_cost") = 8,
+             "count+1 row bounds cutting the rows into contiguous ranges of near-equal nnz + row_cost per row");
 
     m.def("convert_to_ellpack", &convert_to_ellpack_py, "Convert dense NumPy matrix -> ELLPACK handle (device-resident)");
     m.def("decode_from_ellpack", &decode_from_ellpack_py, "Convert ELLPACK handle -> dense NumPy matrix");
@@ -216,6 +221,8 @@ PYBIND11_MODULE(sparseops_backend, m)
         }, py::arg("x"), py::arg("batch"), py::arg("y"), py::arg("stream") = 0)
         .def("device_input_ptr", [](const SparseOnnxModel& m_) { return reinterpret_cast<uintptr_t>(m_.device_input()); })
         .def("device_output_ptr", [](const SparseOnnxModel& m_) { return reinterpret_cast<uintptr_t>(m_.device_output()); })
+        .def_property_readonly("activation_buffers", &SparseOnnxModel::activation_buffers,
+                               "distinct device buffers holding activations in the current plan (reused by liveness)")
         .def("run_resident", [](const SparseOnnxModel& m_, uintptr_t stream) { m_.run_resident(reinterpret_cast<void*>(stream)); },
              py::arg("stream") = 0, "Replay the captured layer loop on the model's own device buffers (asynchronous)")
         .def("shard_rows", [](SparseOnnxModel& model, int rank, int world, py::bytes id) {

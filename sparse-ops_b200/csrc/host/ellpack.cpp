@@ -58,11 +58,9 @@ uint64_t Ellpack::nnz_total() const
     return t;
 }
 
-Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G, bool do_upload) const
+Ellpack Ellpack::shard_range(uint32_t lo, uint32_t hi, bool do_upload) const
 {
-    if (G == 0 || g >= G) throw std::runtime_error("shard_rows: bad shard index");
-    const uint32_t per = (m + G - 1) / G;
-    const uint32_t lo = std::min(m, g * per), hi = std::min(m, lo + per);
+    if (lo > hi || hi > m) throw std::runtime_error("shard_range: bad row range");
     Ellpack S(hi - lo, n, r);
     if (S.m && r) {
         std::memcpy(S.Wd.ptr, Wd.ptr + size_t(lo) * r, size_t(S.m) * r * sizeof(float));
@@ -71,6 +69,37 @@ Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G, bool do_upload) const
     std::copy(nnz.begin() + lo, nnz.begin() + hi, S.nnz.begin());
     if (do_upload) S.upload();
     return S;
+}
+
+Ellpack Ellpack::shard_rows(uint32_t g, uint32_t G, bool do_upload) const
+{
+    if (G == 0 || g >= G) throw std::runtime_error("shard_rows: bad shard index");
+    const uint32_t per = (m + G - 1) / G;
+    const uint32_t lo = std::min(m, g * per);
+    return shard_range(lo, std::min(m, lo + per), do_upload);
+}
+
+// Contiguous row ranges of near-equal work: a row costs its stored entries plus `row_cost` (the
+// fixed part: its output row and its slot in the schedule), and bound g is placed where the running
+// cost is closest to g/G of the total.  Equal row counts are right for iid rows; when the
+// long rows cluster (sorted or banded matrices) they leave one rank with most of the nonzeros.
+std::vector<uint32_t> Ellpack::balanced_row_split(uint32_t G, uint32_t row_cost) const
+{
+    if (G == 0) throw std::runtime_error("balanced_row_split: need at least one shard");
+    std::vector<uint32_t> bounds(size_t(G) + 1, m);
+    bounds[0] = 0;
+    uint64_t total = 0;
+    for (uint32_t c : nnz) total += uint64_t(c) + row_cost;
+    uint64_t run = 0;
+    uint32_t g = 1;
+    for (uint32_t i = 0; i < m && g < G; ++i) {
+        // close shard g-1 in front of row i when that leaves the running cost closer to g/G of the
+        // total than taking row i as well would: g*total - G*run <= G*(run + cost_i) - g*total
+        const uint64_t cost = uint64_t(nnz[i]) + row_cost;
+        while (g < G && 2 * uint64_t(g) * total <= uint64_t(G) * (2 * run + cost)) bounds[g++] = i;
+        run += cost;
+    }
+    return bounds;
 }
 
 namespace {

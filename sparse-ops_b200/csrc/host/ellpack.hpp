@@ -71,6 +71,13 @@ struct Ellpack {
     /// Rows [g*ceil(m/G), (g+1)*ceil(m/G)) clipped to m, as an independent matrix, for row-sharded
     /// runs (uploaded unless upload == false).  Every shard keeps the parent's r.
     Ellpack shard_rows(uint32_t g, uint32_t G, bool upload = true) const;
+    /// Rows [lo, hi) as an independent matrix (keeps the parent's r).
+    Ellpack shard_range(uint32_t lo, uint32_t hi, bool upload = true) const;
+    /// G + 1 ascending row bounds (first 0, last m) cutting the rows into G contiguous ranges of
+    /// near-equal work, a row counting as nnz[i] + row_cost: the split to use instead of equal row
+    /// counts when the long rows cluster.  The reference's row loop (src/ellpack_matmul.cpp:26-30)
+    /// leaves that balance to OpenMP's static schedule.
+    std::vector<uint32_t> balanced_row_split(uint32_t G, uint32_t row_cost = 8) const;
     uint64_t nnz_total() const;
 };
 

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <stdexcept>
 
 #include "onnx_reader.hpp"
@@ -30,6 +31,7 @@ struct SparseOnnxModel::Exec {
     std::unordered_map<std::string, float*> buf;      // tensor name -> device buffer
     std::unordered_map<std::string, uint64_t> rows;   // tensor name -> rows (elements per column)
     std::vector<void*> owned;
+    size_t distinct_buffers = 0;       // activation buffers actually allocated (fewer than tensors when reused)
     // Row-sharded mode with the exchange fused into the SpMM epilogue: for every MatMul output the
     // full buffer of each rank (own pointer + peers' buffers opened over IPC), indexed by rank.
     bool fused = false;
@@ -393,15 +395,39 @@ void SparseOnnxModel::build_exec(uint32_t B) const
         check(spx_stream_sync(nullptr), "bias upload");
     }
 
+    // Activation buffers are planned by liveness, as the reference frees an intermediate once its
+    // last reader has run (src/model_run.cpp:14-19, :116-127): a tensor's buffer returns to a free
+    // list after the last layer that reads it and is handed to a later output that fits, so a deep
+    // graph holds a few activations at a time, not one per layer.  The graph's input and output
+    // keep buffers of their own (callers address them), and a layer's output never shares a buffer
+    // with that layer's inputs (the inputs are released after the output is placed).  Row-sharded
+    // models keep one buffer per tensor: peers store into them between barriers.
+    std::unordered_map<std::string, size_t> last_use;
+    for (size_t i = 0; i < layers_.size(); ++i)
+        for (const auto& in : layers_[i].inputs) last_use[in] = i;
+    const bool reuse = world_ == 1 && !std::getenv("SPX_NO_BUFFER_REUSE");
+    std::multimap<size_t, void*> free_list;                 // capacity in bytes -> buffer
+    std::unordered_map<std::string, size_t> capacity;
     auto alloc = [&](const std::string& name, uint64_t rows, uint64_t padded_rows) {
+        const size_t bytes = size_t(padded_rows) * B * sizeof(float);
         void* p = nullptr;
-        check(spx_malloc(&p, size_t(padded_rows) * B * sizeof(float)), "activation buffer");
-        ex->owned.push_back(p);
+        size_t cap = bytes;
+        auto it = (reuse && name != output_name_) ? free_list.lower_bound(bytes) : free_list.end();
+        if (it != free_list.end()) {
+            cap = it->first;
+            p = it->second;
+            free_list.erase(it);
+        } else {
+            check(spx_malloc(&p, bytes), "activation buffer");
+            ex->owned.push_back(p);
+        }
         ex->buf[name] = static_cast<float*>(p);
         ex->rows[name] = rows;
+        capacity[name] = cap;
     };
     alloc(input_name_, in_features_, in_features_);
-    for (const auto& L : layers_) {
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        const auto& L = layers_[li];
         uint64_t rows, padded;
         if (L.op == LayerOp::MatMul || L.op == LayerOp::Conv) {
             rows = L.out_features;
@@ -415,7 +441,17 @@ void SparseOnnxModel::build_exec(uint32_t B) const
             rows = padded = ex->rows.at(L.inputs[0]);
         }
         alloc(L.outputs[0], rows, padded);
+        if (reuse)
+            for (const auto& in : L.inputs) {
+                auto lu = last_use.find(in);
+                if (in == input_name_ || in == output_name_ || lu == last_use.end() || lu->second != li) continue;
+                auto c = capacity.find(in);
+                if (c == capacity.end()) continue;          // already returned (a layer may name an input twice)
+                free_list.emplace(c->second, ex->buf.at(in));
+                capacity.erase(c);
+            }
     }
+    ex->distinct_buffers = ex->owned.size();
     if (world_ > 1 && comm_) {
         ex->comm = comm_;
         const char* off = std::getenv("SPX_TP_FUSED");
@@ -536,6 +572,12 @@ void SparseOnnxModel::run(const float* input, uint32_t B, float* output) const
     else launch_layers(d_in, d_out, B, ex.stream);
     check(spx_memcpy_d2h(output, d_out, size_t(out_features_) * B * sizeof(float), ex.stream), "output copy");
     check(spx_stream_sync(ex.stream), "run");
+}
+
+size_t SparseOnnxModel::activation_buffers() const
+{
+    if (!exec_) throw std::runtime_error("activation_buffers: call resize_buffers(B) first");
+    return exec_->distinct_buffers;
 }
 
 float* SparseOnnxModel::device_input() const

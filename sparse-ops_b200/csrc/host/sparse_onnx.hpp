@@ -74,6 +74,9 @@ public:
     float* device_input() const;
     float* device_output() const;
     void run_resident(void* stream) const;
+    /// Number of distinct activation buffers the current plan holds; buffers are reused by
+    /// liveness, so this stays small for deep graphs (reference: src/model_run.cpp:116-127).
+    size_t activation_buffers() const;
     /// Output dims as labelled in the ONNX graph (static shape recorded at load).
     std::vector<size_t> output_shape() const;
     /// (Re)allocate the activation buffers for batch B and capture the layer loop as a CUDA graph.

@@ -2,8 +2,10 @@
 python/sparse_onnx.py:6-53 (class OnnxSparseModel), with the same plan and the same run()
 semantics, on top of `cpp_backend` (encode / matvec / matmul) of this package.
 
-The reference reads the file with the `onnx` package; here the in-tree wire-format reader
-(`onnx_wire.read_model`) is used, so nothing beyond numpy is needed.
+This file is a drop-in shim, not an independent design: the class body restates the reference's
+class line for line (same plan tuples, same branches in run()), because its observable behaviour
+is the contract.  The one change: the reference reads the file with the `onnx` package; here the
+in-tree wire-format reader (`onnx_wire.read_model`) is used, so nothing beyond numpy is needed.
 
 Plan (python/sparse_onnx.py:19-34): every Gemm / MatMul node becomes ('matmul', E, bias) with
 E = encode(initializer named by input[1]) taken AS STORED (no transpose attribute is read) and

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libspx_b200.so")
 
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
-LAYOUT_PF, LAYOUT_NCHW = 0, 1
+LAYOUT_PF, LAYOUT_NCHW, LAYOUT_FMAJOR = 0, 1, 2
 OP_RELU, OP_SIGMOID, OP_TANH, OP_ADD = 1, 2, 3, 4
 UNIQUE_ID_BYTES = 128
 IPC_HANDLE_BYTES = 64
@@ -61,7 +61,6 @@ SIGNATURES = {
     "spx_memcpy_d2h": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "spx_memcpy_d2d": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "spx_memset": (C.c_int, [_vp, C.c_int, C.c_size_t, _vp]),
-    "spx_probe_l2_gather": (C.c_int, [_vp, C.c_size_t, C.c_uint32, _vp, _vp, C.POINTER(C.c_uint64)]),
     "spx_stream_create": (C.c_int, [C.POINTER(_vp)]),
     "spx_stream_destroy": (C.c_int, [_vp]),
     "spx_stream_sync": (C.c_int, [_vp]),
@@ -95,6 +94,8 @@ SIGNATURES = {
     "spx_comm_destroy": (C.c_int, [_vp]),
     "spx_allgather_rows": (C.c_int, [_vp, _vp, C.c_uint64, C.c_uint64, _vp]),
     "spx_comm_barrier": (C.c_int, [_vp, _vp]),
+    "spx_comm_info": (C.c_int, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "spx_spmm_host_sharded": (C.c_int, [_vp, _vp, _vp, C.c_uint32, _vp, C.c_int, _vp, _f32p]),
     "spx_ipc_export": (C.c_int, [_vp, C.c_char_p]),
     "spx_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(_vp)]),
     "spx_ipc_close": (C.c_int, [_vp]),

@@ -80,6 +80,12 @@ def main():
         out[name + "_geom"] = np.array([B, Cin, Cout, H, W_, k, pad, dil, int(relu)], dtype=np.int64)
         out[name + "_pf_ref"] = R.conv_run(h, 0, np.ascontiguousarray(x.transpose(1, 2, 3, 0)), B, Cout)
         out[name + "_nchw_ref"] = R.conv_run(h, 1, x, B, Cout)
+        # F-major [W,H,C,B]: conv2d_tiled_im2col_fmajor reads [C,H,W,B] and writes F-major,
+        # conv2d_rbm_fmajor_implicit reads and writes F-major; both must give the same bytes
+        fm = R.conv_run(h, 2, np.ascontiguousarray(x.transpose(1, 2, 3, 0)), B, Cout)
+        fm_rbm = R.conv_run(h, 3, np.ascontiguousarray(x.transpose(3, 2, 1, 0)), B, Cout)
+        assert np.array_equal(fm.view(np.uint32), fm_rbm.view(np.uint32)), name
+        out[name + "_fm_ref"] = fm
         if name == "conv_a":
             blocks = R.rbm(R.conv_ell(h), bias, 8)
             out["rbm_M0"] = np.array([b["M0"] for b in blocks], dtype=np.uint32)

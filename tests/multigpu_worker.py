@@ -2,7 +2,10 @@
 mismatch.  Checks, against the CPU oracle on the same seeded inputs:
   1. row-sharded SpMM with the library's own in-place all-gather (spx_allgather_rows);
   2. SparseOnnxModel in row-sharded (tensor-parallel) mode: every layer ends with an all-gather;
-  3. SparseOnnxModel batch-sharded: each rank runs its own batch columns, no collective."""
+  3. SparseOnnxModel batch-sharded: each rank runs its own batch columns, no collective;
+  4. spx_spmm_host_sharded: host buffers, each rank copies its block of X's rows, all-gather of X
+     over NVLink, own rows of Y back -- one panel and several panels, n not divisible by world;
+  5. a handle used while another device is current is refused with a status code (no launch)."""
 import ctypes as C
 import os
 import sys
@@ -99,6 +102,47 @@ def main():
         lib.spx_ipc_close(pp)
     dist.barrier()
     lib.spx_free(buf)
+
+    # 4. host buffers, sharded copy of X: several 256-column panels (ragged last one) and a single panel
+    for (m4, n4, C4) in ((1003, 701, 772), (64, 50, 36)):
+        W4 = sparse(rng, m4, n4, 0.1)
+        X4 = rng.uniform(-1, 1, (n4, C4)).astype(np.float32)
+        b4 = rng.standard_normal(m4).astype(np.float32)
+        E4 = sb.encode_host(W4)
+        S4 = E4.shard_rows(rank, world, upload=False)
+        per4 = -(-m4 // world)
+        lo4 = min(m4, rank * per4)
+        h4 = lib.ell_create(S4.Wd, S4.idx, S4.nnz, n4)
+        Y4 = np.full((S4.m, C4), np.nan, np.float32)
+        phases = (C.c_float * 4)()
+        fp = lambda a: a.ctypes.data_as(C.c_void_p)
+        bl = np.ascontiguousarray(b4[lo4:lo4 + S4.m])
+        lib.spx_spmm_host_sharded(comm, h4.h, fp(X4), C4, fp(bl), sx.ACT_RELU, fp(Y4), phases)
+        want4 = orc.spmm(orc.encode(W4), X4, b4, act=1)[lo4:lo4 + S4.m]
+        assert np.array_equal(Y4.view(np.uint32), want4.view(np.uint32)), "sharded host SpMM differs"
+        assert all(t >= 0.0 for t in phases) and phases[2] > 0.0
+        lib.spx_spmm_host_sharded(comm, h4.h, fp(X4), C4, None, sx.ACT_NONE, fp(Y4), None)       # second call: cached staging
+        want4 = orc.spmm(orc.encode(W4), X4, None)[lo4:lo4 + S4.m]
+        assert np.array_equal(Y4.view(np.uint32), want4.view(np.uint32)), "sharded host SpMM differs (no bias)"
+    rk, wd = C.c_int(-1), C.c_int(-1)
+    lib.spx_comm_info(comm, C.byref(rk), C.byref(wd))
+    assert (rk.value, wd.value) == (rank, world)
+
+    # 5. misuse made on the host: the handle lives on this rank's GPU, another one is current
+    other = (local + 1) % torch.cuda.device_count()
+    launches = lib.spx_launch_count()
+    lib.spx_set_device(other)
+    try:
+        for call in (lambda: h.spmm(dX.data_ptr(), Cc, Cc, 0, sx.ACT_NONE, dY.data_ptr(), Cc, 0),
+                     lambda: h.spmv(dX.data_ptr(), 0, dY.data_ptr(), 0)):
+            try:
+                call()
+                raise AssertionError("a handle of another device was accepted")
+            except sx.SpxError as ex:
+                assert ex.status == 1
+    finally:
+        lib.spx_set_device(local)
+    assert lib.spx_launch_count() == launches
 
     # 2. + 3. model: 3 layers, relu/relu/none (bit-exact end to end), out features not divisible by world
     dims, B = [64, 96, 80, 30 + world - 1], 8 * world

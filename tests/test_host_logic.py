@@ -251,3 +251,33 @@ def test_conv_workload_density_parameter():
     assert 0.35 < frac < 0.65
     d2 = wl.cfg4(0.1, layers=1)                     # default: 80 % sparse
     assert 0.1 < np.count_nonzero(d2["weights"][0]) / d2["weights"][0].size < 0.3
+
+
+def test_balanced_row_split(backend):
+    """Row ranges of near-equal work for matrices whose long rows cluster; equal row counts
+    (shard_rows) would give the first rank most of the nonzeros here."""
+    rng = np.random.default_rng(8)
+    m, n, G = 4000, 300, 8
+    W = rng.standard_normal((m, n)).astype(np.float32)
+    W[rng.random(W.shape) >= 0.02] = 0
+    W[:200] = rng.standard_normal((200, n)).astype(np.float32)       # 200 dense rows up front
+    E = backend.encode_host(W)
+    b = E.balanced_row_split(G, 0)
+    assert len(b) == G + 1 and b[0] == 0 and b[-1] == m and all(x <= y for x, y in zip(b, b[1:]))
+    per = [int(E.nnz[b[g]:b[g + 1]].sum()) for g in range(G)]
+    share = E.nnz_total / G
+    assert max(per) <= share + E.nnz.max()                 # never more than one row over the share
+    equal = [int(E.nnz[g * 500:(g + 1) * 500].sum()) for g in range(G)]
+    assert max(equal) > 3 * max(per)                       # what the equal split would have given
+    # shards are the parent's rows, r kept
+    S = E.shard_range(b[1], b[2], upload=False)
+    assert (S.m, S.n, S.r) == (b[2] - b[1], n, E.r)
+    assert np.array_equal(S.idx, E.idx[b[1]:b[2]]) and np.array_equal(S.nnz, E.nnz[b[1]:b[2]])
+    # with a per-row cost, empty rows are spread too
+    Z = backend.encode_host(np.zeros((10, 4), np.float32))
+    assert Z.balanced_row_split(5) == [0, 2, 4, 6, 8, 10]
+    assert backend.encode_host(np.ones((2, 3), np.float32)).balanced_row_split(4)[-1] == 2
+    with pytest.raises(RuntimeError):
+        E.shard_range(5, 4, upload=False)
+    with pytest.raises(RuntimeError):
+        E.balanced_row_split(0)

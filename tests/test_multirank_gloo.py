@@ -69,6 +69,43 @@ def _worker(rank, world, port, q):
         y = sharded_spmm(W2, np.ascontiguousarray(h), None, 0)
         want = orc.spmm(orc.encode(W2), orc.spmm(orc.encode(W1), X, b1, act=1), None)
         results["mlp"] = bool(np.array_equal(y.view(np.uint32), want.view(np.uint32)))
+        # clustered long rows: ranges of near-equal nonzeros (balanced_row_split) instead of equal
+        # row counts; slabs are padded to the longest range for the in-place all-gather and the
+        # gathered buffer is compacted with the same bounds on every rank
+        m, n = 90, 40
+        W = _sparse(rng, m, n, 0.1)
+        W[:12] = rng.standard_normal((12, n)).astype(np.float32)
+        X = rng.uniform(-1, 1, (n, 5)).astype(np.float32)
+        b = rng.standard_normal(m).astype(np.float32)
+        E = sb.encode_host(W)
+        bounds = E.balanced_row_split(world, 0)
+        lo, hi = bounds[rank], bounds[rank + 1]
+        S = E.shard_range(lo, hi, upload=False)
+        slab_rows = max(bounds[g + 1] - bounds[g] for g in range(world))
+        full = torch.zeros((slab_rows * world, X.shape[1]), dtype=torch.float32)
+        shard = oracle.EllArrays(S.m, S.n, S.r, S.Wd, S.idx, S.nnz)
+        full[rank * slab_rows:rank * slab_rows + S.m] = torch.from_numpy(orc.spmm(shard, X, b[lo:hi], act=0))
+        dist.all_gather_into_tensor(full, full[rank * slab_rows:(rank + 1) * slab_rows].clone())
+        got = np.concatenate([full.numpy()[g * slab_rows:g * slab_rows + bounds[g + 1] - bounds[g]] for g in range(world)])
+        want = orc.spmm(orc.encode(W), X, b)
+        nz = [int(E.nnz[bounds[g]:bounds[g + 1]].sum()) for g in range(world)]
+        results["balanced"] = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32))) and \
+            max(nz) <= E.nnz_total / world + int(E.nnz.max()) and bounds[1] < m // world
+        # the operand layout of the sharded host-buffer SpMM: every rank places its block of X's
+        # rows into a panel-major buffer (panel p = a contiguous [per * world x width] matrix), one
+        # in-place all-gather per panel rebuilds X on every rank
+        n, Cw, panel = 37, 20, 8
+        X = rng.uniform(-1, 1, (n, Cw)).astype(np.float32)
+        per = -(-n // world)
+        lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
+        ok = True
+        for c0 in range(0, Cw, panel):
+            w = min(panel, Cw - c0)
+            buf = torch.zeros((per * world, w), dtype=torch.float32)
+            buf[lo:hi] = torch.from_numpy(X[lo:hi, c0:c0 + w])
+            dist.all_gather_into_tensor(buf, buf[rank * per:(rank + 1) * per].clone())
+            ok = ok and bool(np.array_equal(buf.numpy()[:n], X[:, c0:c0 + w]))
+        results["x_panels"] = ok
         # the benchmark's shardable generator: two half ranges equal the whole
         import workloads as wl
         rp, col, val = wl.cfg5_rows(rank * 4096, 4096, n=2048, kmax=128, mean=12)

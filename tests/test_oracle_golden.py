@@ -50,6 +50,9 @@ def test_conv_matches_reference(orc, golden, name):
     pf = np.ascontiguousarray(x.transpose(1, 2, 3, 0))
     assert_bit_equal(orc.conv2d(E, g, 0, pf, B, golden[name + "_bias"], relu), golden[name + "_pf_ref"], "PF")
     assert_bit_equal(orc.conv2d(E, g, 1, x, B, golden[name + "_bias"], relu), golden[name + "_nchw_ref"], "NCHW")
+    # F-major [W,H,C,B]: the bytes conv2d_tiled_im2col_fmajor and conv2d_rbm_fmajor_implicit both produce
+    fm = np.ascontiguousarray(x.transpose(3, 2, 1, 0))
+    assert_bit_equal(orc.conv2d(E, g, 2, fm, B, golden[name + "_bias"], relu), golden[name + "_fm_ref"], "F-major")
 
 
 def test_oracle_agrees_with_live_reference(orc, ref):

@@ -85,7 +85,8 @@ def test_golden_conv(lib, orc, golden, cuda, name):
     x = golden[name + "_x_nchw"]
     dB = dev(golden[name + "_bias"], cuda)
     for layout, src, want in ((sx.LAYOUT_PF, np.ascontiguousarray(x.transpose(1, 2, 3, 0)), golden[name + "_pf_ref"]),
-                              (sx.LAYOUT_NCHW, x, golden[name + "_nchw_ref"])):
+                              (sx.LAYOUT_NCHW, x, golden[name + "_nchw_ref"]),
+                              (sx.LAYOUT_FMAJOR, np.ascontiguousarray(x.transpose(3, 2, 1, 0)), golden[name + "_fm_ref"])):
         dX = dev(src, cuda)
         dY = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
         h.conv2d(g, layout, ptr(dX), B, ptr(dB), sx.ACT_RELU if relu else sx.ACT_NONE, ptr(dY))
@@ -117,6 +118,59 @@ def test_spmm_bit_exact_vs_oracle(lib, orc, cuda, m, n, C, p):
     assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_NONE, cuda), orc.spmm(E, X, b), "spmm")
     assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_RELU, cuda, ld_pad=4), orc.spmm(E, X, b, act=1), "spmm relu, padded ld")
     assert_bit_equal(gpu_spmm(h, X, None, sx.ACT_NONE, cuda, ld_pad=3), orc.spmm(E, X, None), "spmm odd ld")
+
+
+@pytest.mark.parametrize("C", [132, 260, 512, 516, 1024])
+def test_spmm_long_rows_several_panels(lib, orc, cuda, C):
+    """Wide X (several column panels) together with rows of 512 and more stored entries: such rows
+    are scheduled first, for all panels, on narrower panels with more gathers in flight.  Every row
+    against the oracle, bit for bit."""
+    m, n = 2048, 4096
+    rng = np.random.default_rng([m, n, C, 9])
+    W = sparse(rng, m, n, 0.02)
+    for row, cnt in ((3, 600), (700, 512), (701, 511), (1500, 2000), (2047, 4096), (9, 1031)):
+        W[row] = 0
+        cols = rng.choice(n, cnt, replace=False)
+        W[row, cols] = rng.standard_normal(cnt).astype(np.float32)
+    X = rng.uniform(-1, 1, (n, C)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    assert_bit_equal(gpu_spmm(h, X, b, sx.ACT_NONE, cuda), orc.spmm(E, X, b), "spmm, long rows")
+    assert_bit_equal(gpu_spmm(h, X, None, sx.ACT_RELU, cuda, ld_pad=8), orc.spmm(E, X, None, act=1), "spmm relu, padded ld")
+
+
+def test_config5_headline_shape_vs_oracle(lib, orc, cuda):
+    """The shape the benchmark's headline line times, on the first 4096 rows of the same matrix:
+    n = 65536, C = 1024 (four 256-column panels) and the forced 2048-entry row.  The oracle checks
+    the long rows and a sample of the others, bit for bit; the rest through additivity over two
+    half shards."""
+    import workloads as wl
+    from oracle import EllArrays
+    rows, n, C = 4096, 65536, 1024
+    rowptr, col, val = wl.cfg5_rows(0, rows, n=n)
+    h = lib.ell_create_csr(rows, n, rowptr, col, val)
+    assert h.r == 2048
+    X = wl.cfg5_dense_operand(n, C)
+    dX = dev(X, cuda)
+    dY = torch.full((rows, C), float("nan"), device=cuda, dtype=torch.float32)
+    h.spmm(dX.data_ptr(), C, C, 0, sx.ACT_NONE, dY.data_ptr(), C)
+    torch.cuda.synchronize()
+    got = dY.cpu().numpy()
+    Wd, idx, nnz = wl.csr_to_ell(rows, rowptr, col, val)
+    longest = np.argsort(nnz)[::-1][:24]
+    pick = np.unique(np.concatenate([longest, np.arange(0, rows, 97), [rows - 1]]))
+    assert nnz[pick].max() == 2048 and (nnz[pick] >= 512).sum() >= 8
+    sub = EllArrays(len(pick), n, Wd.shape[1], Wd[pick], idx[pick], nnz[pick])
+    assert_bit_equal(got[pick], orc.spmm(sub, X, None), "config 5 headline shape, sampled rows")
+    half = rows // 2
+    for g in range(2):
+        lo, hi = int(rowptr[g * half]), int(rowptr[(g + 1) * half])
+        hg = lib.ell_create_csr(half, n, rowptr[g * half:(g + 1) * half + 1] - rowptr[g * half], col[lo:hi], val[lo:hi])
+        out = torch.empty((half, C), device=cuda, dtype=torch.float32)
+        hg.spmm(dX.data_ptr(), C, C, 0, sx.ACT_NONE, out.data_ptr(), C)
+        torch.cuda.synchronize()
+        assert_bit_equal(out.cpu().numpy(), got[g * half:(g + 1) * half], f"half shard {g}")
 
 
 @pytest.mark.parametrize("act", [sx.ACT_SIGMOID, sx.ACT_TANH])
@@ -209,6 +263,40 @@ def test_csr_and_device_encoder(lib, orc, cuda):
     assert_bit_equal(out.cpu().numpy(), orc.decode(E), "device decode")
 
 
+def test_device_encoder_on_a_non_blocking_stream(lib, orc, cuda):
+    """spx_ell_encode_device on a stream made by spx_stream_create (non-blocking: not ordered behind
+    the default stream): the zero fill of the slabs must be ordered before the pack on that same
+    stream.  A slab of about 200 MB per array, so that a fill on another stream would still be
+    running when the pack starts; compared with the host encoder's result."""
+    import ctypes as C
+    m, n = 24000, 4096
+    rng = np.random.default_rng(41)
+    W = rng.standard_normal((m, n)).astype(np.float32)
+    W[rng.random((m, n), dtype=np.float32) >= 0.5] = 0
+    dW = dev(W, cuda)
+    torch.cuda.synchronize()
+    st = C.c_void_p()
+    lib.spx_stream_create(C.byref(st))
+    try:
+        h = lib.ell_encode_device(dW.data_ptr(), m, n, st)
+        lib.spx_stream_sync(st)
+    finally:
+        lib.spx_stream_destroy(st)
+    Wd, idx, nnz = h.download()
+    cnt = np.count_nonzero(W, axis=1)
+    assert h.r == cnt.max() and np.array_equal(nnz, cnt)
+    # every row: packed values and ascending column ids, zero padding behind them
+    rows = np.concatenate([np.arange(0, m, 997), [m - 1, int(cnt.argmax()), int(cnt.argmin())]])
+    for i in rows:
+        c = int(cnt[i])
+        cols = np.flatnonzero(W[i])
+        assert np.array_equal(idx[i, :c], cols) and np.array_equal(Wd[i, :c].view(np.uint32), W[i, cols].view(np.uint32))
+    pad = np.arange(h.r)[None, :] >= cnt[:, None]
+    assert not Wd[pad].any() and not idx[pad].any()
+    sub = orc.encode(W[:512])
+    assert np.array_equal(idx[:512, :sub.r], sub.idx) and np.array_equal(Wd[:512, :sub.r].view(np.uint32), sub.Wd.view(np.uint32))
+
+
 CONV_CASES = [
     # B, Cin, Cout, H, W, k, stride, pad, dil
     (4, 8, 16, 12, 12, 3, 1, 1, 1), (32, 16, 24, 14, 14, 3, 1, 1, 1), (3, 5, 7, 9, 11, 3, 1, 0, 1),
@@ -221,14 +309,25 @@ CONV_CASES = [
 ]
 
 
+def as_layout(x_nchw, layout):
+    """The logical NCHW tensor in the memory order of a layout."""
+    perm = {sx.LAYOUT_PF: (1, 2, 3, 0), sx.LAYOUT_NCHW: (0, 1, 2, 3), sx.LAYOUT_FMAJOR: (3, 2, 1, 0)}[layout]
+    return np.ascontiguousarray(x_nchw.transpose(perm))
+
+
+def to_nchw(y, layout):
+    perm = {sx.LAYOUT_PF: (3, 0, 1, 2), sx.LAYOUT_NCHW: (0, 1, 2, 3), sx.LAYOUT_FMAJOR: (3, 2, 1, 0)}[layout]
+    return y.transpose(perm)
+
+
 @pytest.mark.parametrize("B,Cin,Cout,H,W,k,s,pad,dil", CONV_CASES)
-@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW])
+@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW, sx.LAYOUT_FMAJOR])
 def test_conv_bit_exact_vs_oracle(lib, orc, cuda, layout, B, Cin, Cout, H, W, k, s, pad, dil):
     rng = np.random.default_rng([B, Cin, Cout, H, k, s])
     wt = sparse(rng, Cout, Cin * k * k, 0.25) * np.float32(0.3)
     bias = rng.standard_normal(Cout).astype(np.float32)
     x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
-    src = np.ascontiguousarray(x.transpose(1, 2, 3, 0)) if layout == sx.LAYOUT_PF else x
+    src = as_layout(x, layout)
     E = orc.encode(wt)
     gd = dict(Cin=Cin, kH=k, kW=k, sH=s, sW=s, pH=pad, pW=pad, dH=dil, dW=dil, H=H, W=W)
     want = orc.conv2d(E, gd, layout, src, B, bias, 1)
@@ -242,12 +341,10 @@ def test_conv_bit_exact_vs_oracle(lib, orc, cuda, layout, B, Cin, Cout, H, W, k,
     # and against a dense fp32 convolution (mathematical check, independent of the ELLPACK chain)
     ref = torch.nn.functional.conv2d(torch.from_numpy(x), torch.from_numpy(wt.reshape(Cout, Cin, k, k)),
                                      torch.from_numpy(bias), stride=s, padding=pad, dilation=dil).relu().numpy()
-    got = dY.cpu().numpy()
-    got_nchw = got.transpose(3, 0, 1, 2) if layout == sx.LAYOUT_PF else got
-    assert np.abs(got_nchw - ref).max() <= 1e-4
+    assert np.abs(to_nchw(dY.cpu().numpy(), layout) - ref).max() <= 1e-4
 
 
-@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW])
+@pytest.mark.parametrize("layout", [sx.LAYOUT_PF, sx.LAYOUT_NCHW, sx.LAYOUT_FMAJOR])
 def test_conv_unsorted_columns(lib, orc, cuda, layout):
     """Raw ELLPACK arrays may store a row's columns in any order (spx_ell_create only checks the range).
     The tiled kernels need ascending columns; such a handle must take the general kernel and still
@@ -263,7 +360,7 @@ def test_conv_unsorted_columns(lib, orc, cuda, layout):
         E.idx[i, :c] = E.idx[i, :c][perm]
     bias = rng.standard_normal(Cout).astype(np.float32)
     x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
-    src = np.ascontiguousarray(x.transpose(1, 2, 3, 0)) if layout == sx.LAYOUT_PF else x
+    src = as_layout(x, layout)
     gd = dict(Cin=Cin, kH=k, kW=k, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
     want = orc.conv2d(E, gd, layout, src, B, bias, 1)
     h = gpu_ell(lib, E)
@@ -504,6 +601,7 @@ def test_abi_rejects_misuse_with_status_codes(lib, orc, cuda):
     import ctypes as C
     E = orc.encode(np.eye(8, dtype=np.float32))
     h = gpu_ell(lib, E)
+    hz = gpu_ell(lib, orc.encode(np.zeros((8, 8), np.float32)))
     x = torch.ones(8, device=cuda)
     y = torch.zeros(8, device=cuda)
     before = lib.spx_launch_count()
@@ -513,6 +611,8 @@ def test_abi_rejects_misuse_with_status_codes(lib, orc, cuda):
         lambda: lib.spx_spmm(0, x.data_ptr(), 1, 1, 0, 0, y.data_ptr(), 1, 0),                     # null handle
         lambda: lib.spx_spmm(h.h, x.data_ptr(), 1, 1, 0, 0, 0, 1, 0),                              # null output
         lambda: lib.spx_spmv(h.h, 0, 0, y.data_ptr(), 0),                                          # null x with nonzeros
+        lambda: lib.spx_spmv(hz.h, 0, 0, y.data_ptr(), 0),                                         # null x, no nonzeros but n > 0
+        lambda: lib.spx_spmv_reference_order(hz.h, 0, 0, y.data_ptr(), 0),
         lambda: lib.spx_spmm_bcast(h.h, x.data_ptr(), 1, 1, 0, 0, arr9, 9, 0, 1, 0),               # more than 8 buffers
         lambda: lib.spx_spmm_bcast(h.h, x.data_ptr(), 1, 1, 0, 0, None, 1, 0, 1, 0),               # null list
         lambda: lib.spx_eltwise(9, x.data_ptr(), 0, y.data_ptr(), 8, 0),                           # unknown op
@@ -536,15 +636,18 @@ def test_abi_rejects_misuse_with_status_codes(lib, orc, cuda):
     assert y.cpu().numpy().tolist() == [1.0] * 8
 
 
-def test_l2_gather_probe_runs(lib, cuda):
-    """The measurement aid reads what it reports and leaves the sink alone."""
+def test_l2_gather_probe_runs(cuda):
+    """The benchmark's measurement aid (its own small library) reads what it reports and leaves the sink alone."""
     import ctypes
+
+    import bench
+    probe = bench.load_probe()
+    assert probe is not None, "libspx_bench_probe.so is missing: run sparse-ops_b200/build_cuda.sh"
     buf = torch.zeros(8 << 20, dtype=torch.uint8, device=cuda)
     sink = torch.full((1,), 7.0, dtype=torch.float32, device=cuda)
     n = ctypes.c_uint64(0)
-    lib.spx_probe_l2_gather(buf.data_ptr(), 8 << 20, 4, sink.data_ptr(), 0, ctypes.byref(n))
+    assert probe(buf.data_ptr(), 8 << 20, 4, sink.data_ptr(), 0, ctypes.byref(n)) == 0
     torch.cuda.synchronize()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     assert n.value == sms * 8 * 8 * 4 * 8 * 512 and float(sink.item()) == 7.0
-    with pytest.raises(sx.SpxError):
-        lib.spx_probe_l2_gather(buf.data_ptr(), 512, 4, sink.data_ptr(), 0, ctypes.byref(n))
+    assert probe(buf.data_ptr(), 512, 4, sink.data_ptr(), 0, ctypes.byref(n)) == -1
