@@ -397,8 +397,6 @@ int spx_ell_destroy(spx_ell* e)
     cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch); cudaFree(e->fm_scratch);
     for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
     for (cudaEvent_t ev : e->pipe_events) if (ev) cudaEventDestroy(ev);
-    if (e->aside_stream) cudaStreamDestroy(e->aside_stream);
-    for (cudaEvent_t ev : e->aside_ev) if (ev) cudaEventDestroy(ev);
     delete e;
     return SPX_OK;
 }

@@ -7,7 +7,6 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
-#include <mutex>
 
 #include "spx_b200.h"
 
@@ -49,11 +48,6 @@ struct spx_ell {
     // table, built on the first spx_spmv of such a handle.  spmv_win == UINT32_MAX: not applicable.
     uint32_t* spmv_split = nullptr;
     uint32_t spmv_win = 0;
-    // Second stream (highest priority) and the fork / join events of the SpMM that launches its
-    // long rows aside (spmm.cu), created on first use.
-    cudaStream_t aside_stream = nullptr;
-    cudaEvent_t aside_ev[2] = {nullptr, nullptr};
-    std::mutex aside_mu;
     // Pinned + device staging for the host-buffer entry points (abi.cu), grown on demand.
     void* stage_dev = nullptr;
     size_t stage_dev_bytes = 0;

@@ -19,7 +19,6 @@
 
 #include <algorithm>
 #include <cstdlib>
-#include <mutex>
 
 namespace {
 
@@ -143,6 +142,152 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
             for (int g = 0; g < kMaxPeers; ++g)
                 if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// spmm_gather_staged: the kernel for matrices whose longest rows decide the duration (few rows
+// per GPU, skewed lengths: a row shard of a power-law matrix).  Same chain per output element
+// as spmm_gather_vec.  Differences: (1) the first `head` row blocks of the schedule -- the rows
+// with 512 and more stored entries -- are issued first, for all their panels, and run on
+// 128-column panels with eight rows of X in flight per round trip; all other row blocks follow
+// panel-major on 256-column panels with four.  (2) A row's (w, idx) slab travels 32 entries at a
+// time, one batch ahead, through a double-buffered 256-byte staging area of the warp in shared
+// memory (cp.async) and is handed to the lanes with 16-byte broadcast loads, one per four
+// entries, instead of two shuffles per entry: the chain of a long row no longer waits for slab
+// reads.  (3) Loads and FMAs carry the predicate "entry exists"; nothing is zero-filled.
+// ---------------------------------------------------------------------------------------
+struct StagedMap {
+    uint32_t blocks;        // grid size
+    uint32_t row_blocks;    // row blocks (one row per warp)
+    uint32_t head;          // row blocks on the narrow path, issued first, panel-minor
+    uint32_t head_panels;   // 128-column panels
+    uint32_t panels;        // 256-column panels of the wide path
+};
+
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// One row on one panel of 128 * NV columns, G rows of X per round trip; the lane owns columns
+// c0 + 128 * v + 0..3.
+template <int NV, int G>
+__device__ __forceinline__ void staged_row(const float* __restrict__ w, const uint32_t* __restrict__ k, uint32_t nn,
+                                           const float* __restrict__ X, uint32_t c0, uint32_t C, uint32_t ldxb, float b, int act,
+                                           const PeerOut& out, size_t out_at, float* sw, uint32_t* sk, int lane)
+{
+    static_assert(G % 4 == 0 && 32 % G == 0, "groups are made of 16-byte quads");
+    bool on[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) on[v] = (c0 + 128u * v) < C;   // C % 4 == 0 on this path
+    float4 acc[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) acc[v] = make_float4(b, b, b, b);
+    const char* xbase = reinterpret_cast<const char*>(X + c0);
+
+    if ((uint32_t)lane < nn) {
+        cp_async4(sw + lane, w + lane);
+        cp_async4(sk + lane, k + lane);
+    }
+    cp_async_commit();
+    const uint32_t batches = (nn + 31) >> 5;
+    for (uint32_t bt = 0; bt < batches; ++bt) {
+        const float* bw = sw + (bt & 1) * 32;
+        const uint32_t* bk = sk + (bt & 1) * 32;
+        cp_async_wait_all();
+        __syncwarp();       // batch bt has landed for all lanes; the other buffer is no longer read
+        const uint32_t jn = (bt + 1) * 32 + lane;
+        if (jn < nn) {      // next batch in flight while this one is multiplied
+            cp_async4(sw + ((bt + 1) & 1) * 32 + lane, w + jn);
+            cp_async4(sk + ((bt + 1) & 1) * 32 + lane, k + jn);
+        }
+        cp_async_commit();
+        const uint32_t cnt = min(32u, nn - bt * 32);
+        for (uint32_t t = 0; t < cnt; t += G) {
+            float wt[G];
+            uint32_t kt[G];
+#pragma unroll
+            for (int q = 0; q < G / 4; ++q) {
+                const float4 w4 = *reinterpret_cast<const float4*>(bw + t + 4 * q);
+                const uint4 k4 = *reinterpret_cast<const uint4*>(bk + t + 4 * q);
+                wt[4 * q] = w4.x; wt[4 * q + 1] = w4.y; wt[4 * q + 2] = w4.z; wt[4 * q + 3] = w4.w;
+                kt[4 * q] = k4.x; kt[4 * q + 1] = k4.y; kt[4 * q + 2] = k4.z; kt[4 * q + 3] = k4.w;
+            }
+            const uint32_t left = cnt - t;
+            float4 xv[G][NV];
+#pragma unroll
+            for (int u = 0; u < G; ++u) {       // issue all gathers of the group first
+                if ((uint32_t)u < left) {
+                    const char* xr = xbase + (size_t)kt[u] * ldxb;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v)
+                        if (on[v]) xv[u][v] = __ldg(reinterpret_cast<const float4*>(xr + 512 * v));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < G; ++u) {       // then the FMA chain, strictly in storage order
+                if ((uint32_t)u < left) {
+#pragma unroll
+                    for (int v = 0; v < NV; ++v)
+                        if (on[v]) fma4(acc[v], wt[u], xv[u][v]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        if (on[v]) {
+            float4 o = acc[v];
+            if (act != SPX_ACT_NONE) {
+                o.x = spx::apply_act(o.x, act); o.y = spx::apply_act(o.y, act);
+                o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
+            }
+            const size_t at = out_at + 128 * v;
+#pragma unroll
+            for (int g = 0; g < kMaxPeers; ++g)
+                if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kGatherWarps * 32, 4)
+spmm_gather_staged(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+                   const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                   uint32_t m, uint32_t pitch,
+                   const float* __restrict__ X, uint32_t C, uint32_t ldxb,
+                   const float* __restrict__ bias, int act, PeerOut out, uint64_t ldy, StagedMap sm)
+{
+    extern __shared__ __align__(16) float s_stage[];           // per warp: 64 weights, then 64 column ids
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* s_w = s_stage + warp * 128;
+    uint32_t* s_k = reinterpret_cast<uint32_t*>(s_w + 64);
+    const uint32_t head_blocks = sm.head * sm.head_panels;
+    const bool narrow = blockIdx.x < head_blocks;
+    uint32_t rb, panel;
+    if (narrow) {
+        rb = blockIdx.x / sm.head_panels;
+        panel = blockIdx.x % sm.head_panels;
+    } else {
+        const uint32_t t = blockIdx.x - head_blocks, rest = sm.row_blocks - sm.head;
+        panel = t / rest;
+        rb = sm.head + t % rest;
+    }
+    const uint32_t slot = rb * (blockDim.x >> 5) + warp;
+    if (slot >= m) return;                      // whole warp leaves together
+    const uint32_t row = __ldg(row_order + slot);
+    const float b = bias ? __ldg(bias + row) : 0.0f;
+    const uint32_t nn = __ldg(nnz + row);
+    const float* __restrict__ w = Wd + (size_t)row * pitch;
+    const uint32_t* __restrict__ k = idx + (size_t)row * pitch;
+    const size_t out_row = (size_t)(out.row0 + row) * ldy;
+    if (narrow) {
+        const uint32_t c0 = panel * 128u + 4u * lane;
+        staged_row<1, 8>(w, k, nn, X, c0, C, ldxb, b, act, out, out_row + c0, s_w, s_k, lane);
+    } else {
+        const uint32_t c0 = panel * 256u + 4u * lane;
+        staged_row<2, 4>(w, k, nn, X, c0, C, ldxb, b, act, out, out_row + c0, s_w, s_k, lane);
     }
 }
 
@@ -431,66 +576,20 @@ static BlockMap block_map(const spx_ell* e, uint32_t C, uint32_t panels, uint32_
     return bm;
 }
 
-// Whether the long rows should run as a launch of their own (see launch_spmm_bcast).  Estimates:
-// the kernel moves 4*C bytes of X per stored entry at about 17 TB/s; the longest row's chain takes
-// max_nnz / 4 round trips of about 1.2 us on the wide path.  SPX_SPMM_SPLIT=0|1 overrides.
-static bool split_long_rows(const spx_ell* e, uint32_t C)
+// Whether the longest row's chain of gathers decides the kernel's duration (see
+// spmm_gather_staged).  Estimates: the kernel moves 4*C bytes of X per stored entry at about
+// 17 TB/s; the longest row's chain takes max_nnz / 4 round trips of about 1.2 us on the wide path.
+// Measured on B200 (power-law rows, mean 64, max 2048, n = 65536, C = 1024), staged kernel against
+// spmm_gather_vec: 32768 rows 0.556 against 0.610 ms, 65536 rows 1.00 against 1.00 ms, 262144 rows
+// 4.21 against 4.09 ms.  SPX_SPMM_STAGED=0|1 overrides.
+static bool chain_bound(const spx_ell* e, uint32_t C)
 {
-    static const int forced = [] { const char* v = getenv("SPX_SPMM_SPLIT"); return v ? atoi(v) : -1; }();
-    if (e->long_rows == 0 || e->long_rows >= e->m || C <= 128) return false;
+    static const int forced = [] { const char* v = getenv("SPX_SPMM_STAGED"); return v ? atoi(v) : -1; }();
+    if (e->long_rows == 0 || C <= 128) return false;
     if (forced >= 0) return forced != 0;
     const double kernel_us = (double)e->nnz_total * C * 4.0 / 17e6 * (148.0 / sm_count(e->device));
     const double chain_us = e->max_nnz / 4.0 * 1.2;
-    return chain_us > 0.25 * kernel_us;
-}
-
-// Long rows on the handle's second stream, narrow panels; all other rows on `s`, wide panels.
-// Fork and join are events, so the pair also records into a stream capture as two parallel nodes.
-static int launch_long_rows_aside(const spx_ell* ce, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
-                                  const PeerOut& out, uint64_t ldy, cudaStream_t s)
-{
-    spx_ell* e = const_cast<spx_ell*>(ce);
-    std::lock_guard<std::mutex> lk(e->aside_mu);       // one fork / join at a time per handle
-    if (!e->aside_stream) {
-        int lo = 0, hi = 0;
-        if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess ||
-            cudaStreamCreateWithPriority(&e->aside_stream, cudaStreamNonBlocking, hi) != cudaSuccess ||
-            cudaEventCreateWithFlags(&e->aside_ev[0], cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&e->aside_ev[1], cudaEventDisableTiming) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return -1;
-        }
-    }
-    SPX_CUDA(cudaEventRecord(e->aside_ev[0], s));
-    SPX_CUDA(cudaStreamWaitEvent(e->aside_stream, e->aside_ev[0], 0));
-    {   // rows 0 .. long_rows-1 of the schedule
-        const uint32_t panels = (C + 127) / 128, rows = e->long_rows;
-        const uint32_t wpb = rows >= 8 ? 8 : rows >= 4 ? 4 : 2;
-        BlockMap bm{};
-        bm.row_blocks = (rows + wpb - 1) / wpb;
-        bm.panels = panels;
-        bm.head = bm.row_blocks;                         // panel-minor: every long row starts on all panels at once
-        bm.blocks = bm.row_blocks * panels;
-        spmm_gather_vec<1, 8, 4><<<bm.blocks, wpb * 32, 0, e->aside_stream>>>(e->Wd, e->idx, e->nnz, e->row_order, rows, e->pitch,
-                                                                            X, C, ldx, bias, act, out, ldy, bm);
-        SPX_LAUNCH_CHECK("spmm_gather_vec");
-    }
-    SPX_CUDA(cudaEventRecord(e->aside_ev[1], e->aside_stream));
-    {   // the remaining rows
-        const uint32_t panels = (C + 255) / 256, rows = e->m - e->long_rows;
-        uint32_t wpb = 8;
-        while (wpb > 2 && (uint64_t)((rows + wpb - 1) / wpb) * panels < (uint64_t)sm_count(e->device) * 8) wpb >>= 1;
-        BlockMap bm{};
-        bm.row_blocks = (rows + wpb - 1) / wpb;
-        bm.panels = panels;
-        bm.head = 0;
-        bm.blocks = bm.row_blocks * panels;
-        spmm_gather_vec<2, 4, 4><<<bm.blocks, wpb * 32, 0, s>>>(e->Wd, e->idx, e->nnz, e->row_order + e->long_rows, rows, e->pitch,
-                                                              X, C, ldx, bias, act, out, ldy, bm);
-        SPX_LAUNCH_CHECK("spmm_gather_vec");
-    }
-    SPX_CUDA(cudaStreamWaitEvent(s, e->aside_ev[1], 0));
-    return SPX_OK;
+    return chain_us > 0.4 * kernel_us;
 }
 
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
@@ -554,13 +653,21 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
         const int nv = gather_nv(e->n, C);
         // A row is one dependent chain of gathers, G rows of X per round trip to L2 (about a
         // microsecond under load).  When the longest row's chain is a large part of the whole
-        // kernel (few rows per GPU, skewed lengths) it becomes the tail: the rows with 512 and
-        // more entries then go out as a launch of their own on a second stream, on 128-column
-        // panels with eight rows of X in flight per round trip (half the round trips), while the
-        // remaining rows run next to them on the caller's stream.
-        if (nv == 2 && split_long_rows(e, C)) {
-            int rc = launch_long_rows_aside(e, X, C, ldx, bias, act, out, ldy, s);
-            if (rc != -1) return rc;            // -1: the second stream could not be set up
+        // kernel (few rows per GPU, skewed lengths) it becomes the tail: spmm_gather_staged then
+        // gives the rows with 512 and more entries 128-column panels with eight rows of X in
+        // flight per round trip (half the round trips), issued first.
+        if (nv == 2 && ldx < (1ull << 30) && chain_bound(e, C)) {
+            const uint32_t wpb = gather_wpb(e, (C + 255) / 256);
+            StagedMap sm{};
+            sm.row_blocks = (e->m + wpb - 1) / wpb;
+            sm.panels = (C + 255) / 256;
+            sm.head_panels = (C + 127) / 128;
+            sm.head = std::min<uint32_t>(sm.row_blocks, (e->long_rows + wpb - 1) / wpb);
+            sm.blocks = sm.head * sm.head_panels + (sm.row_blocks - sm.head) * sm.panels;
+            spmm_gather_staged<<<sm.blocks, wpb * 32, (size_t)wpb * 512, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
+                                                                          X, C, (uint32_t)(ldx * 4), bias, act, out, ldy, sm);
+            SPX_LAUNCH_CHECK("spmm_gather_staged");
+            return SPX_OK;
         }
         const uint32_t panels = (C + 128 * nv - 1) / (128 * nv);
         const uint32_t wpb = gather_wpb(e, panels);

@@ -27,15 +27,83 @@ __device__ __forceinline__ float group_sum(float v) {
     return v;
 }
 
-// Small matrices are latency-bound: staging x, the row schedule, the row length and the slabs
-// would be four memory round trips in a row.  So the kernel is software-pipelined: a group asks
+template <int LPR, bool SMEM>
+__global__ void __launch_bounds__(1024)
+spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+                const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
+                uint32_t m, uint32_t n, uint32_t pitch,
+                const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y)
+{
+    extern __shared__ __align__(16) float xs[];
+    if (SMEM) {
+        // n floats, 16-byte vectors where alignment allows
+        const uint32_t n4 = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? (n >> 2) : 0;
+        for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x)
+            reinterpret_cast<float4*>(xs)[i] = __ldg(reinterpret_cast<const float4*>(x) + i);
+        for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) xs[i] = __ldg(x + i);
+        __syncthreads();
+    }
+    const float* __restrict__ xsrc = SMEM ? xs : x;
+
+    const uint32_t lane = threadIdx.x & (LPR - 1);
+    const uint32_t groups_per_block = blockDim.x / LPR;
+    const uint32_t group = blockIdx.x * groups_per_block + threadIdx.x / LPR;
+    const uint32_t stride = gridDim.x * groups_per_block;
+    // All lanes of a warp run the same number of row iterations so that the shuffles below
+    // always see the full warp.
+    const uint32_t iters = (m + stride - 1) / stride;
+
+    for (uint32_t it = 0; it < iters; ++it) {
+        // slots of the sorted row schedule are dealt round-robin: every group gets long and short rows
+        const uint32_t slot = group + it * stride;
+        const bool live = slot < m;
+        const uint32_t row = live ? __ldg(row_order + slot) : 0u;
+        const uint32_t nn = live ? __ldg(nnz + row) : 0u;
+        const float4* __restrict__ w4 = reinterpret_cast<const float4*>(Wd + (size_t)row * pitch);
+        const uint4* __restrict__ k4 = reinterpret_cast<const uint4*>(idx + (size_t)row * pitch);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        // UNR 16-byte vectors of Wd and of idx in flight per lane; entries >= nn are padding and
+        // are neither loaded nor multiplied
+        constexpr int UNR = 4;
+        for (uint32_t j = lane * 4; j < nn; j += LPR * 4 * UNR) {
+            float4 wv[UNR];
+            uint4 kv[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const uint32_t ju = j + u * LPR * 4;
+                if (ju < nn) {
+                    wv[u] = __ldcs(w4 + (ju >> 2));
+                    kv[u] = __ldcs(k4 + (ju >> 2));
+                } else {
+                    wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    kv[u] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const uint32_t ju = j + u * LPR * 4;
+                if (ju < nn) a0 = fmaf(wv[u].x, xsrc[kv[u].x], a0);
+                if (ju + 1 < nn) a1 = fmaf(wv[u].y, xsrc[kv[u].y], a1);
+                if (ju + 2 < nn) a2 = fmaf(wv[u].z, xsrc[kv[u].z], a2);
+                if (ju + 3 < nn) a3 = fmaf(wv[u].w, xsrc[kv[u].w], a3);
+            }
+        }
+        float acc = (a0 + a1) + (a2 + a3);
+        acc = group_sum<LPR>(acc);
+        if (live && lane == 0) y[row] = (bias ? __ldg(bias + row) : 0.0f) + acc;
+    }
+}
+
+// spmv_ell_small_kernel: matrices of a few thousand columns (x up to 32 KB).  They are
+// latency-bound: staging x, the row schedule, the row length and the slabs would be four memory
+// round trips in a row.  So this kernel is software-pipelined: a group asks
 // for its first row's id and length and for that row's first slab vectors BEFORE x is staged (none
 // of them depends on x), and while a row is summed the next row's id, length and first vectors
 // are already in flight.  row_order may be null (rows of near-equal length): slot == row then, and
 // one dependent load goes away.
-template <int LPR, bool SMEM>
+template <int LPR>
 __global__ void __launch_bounds__(1024)
-spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
+spmv_ell_small_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 const uint32_t* __restrict__ nnz, const uint32_t* __restrict__ row_order,
                 uint32_t m, uint32_t n, uint32_t pitch,
                 const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y)
@@ -76,7 +144,7 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
     uint32_t nn = live ? __ldg(nnz + row) : 0u;
     load_chunk(row, nn, lane * 4);
 
-    if (SMEM) {
+    {
         // n floats, 16-byte vectors where alignment allows
         const uint32_t n4 = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? (n >> 2) : 0;
         for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x)
@@ -84,7 +152,7 @@ spmv_ell_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
         for (uint32_t i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) xs[i] = __ldg(x + i);
         __syncthreads();
     }
-    const float* __restrict__ xsrc = SMEM ? xs : x;
+    const float* __restrict__ xsrc = xs;
 
     for (uint32_t it = 0; it < iters; ++it) {
         // the next row's id and length travel while this row is summed
@@ -250,6 +318,22 @@ spmv_reforder_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ 
     if (live && l == 0) y[row] = (bias ? __ldg(bias + row) : 0.0f) + a;
 }
 
+constexpr size_t kSmallX = 32 * 1024;
+
+template <int LPR, bool SMEM>
+int launch_one(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s,
+               int threads, int blocks, size_t smem)
+{
+    auto kfn = spmv_ell_kernel<LPR, SMEM>;
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return spx::fail(SPX_ERR_CUDA, "spmv: shared memory opt-in failed: %s", cudaGetErrorString(err));
+    }
+    kfn<<<blocks, threads, smem, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->n, e->pitch, x, bias, y);
+    SPX_LAUNCH_CHECK("spmv_ell_kernel");
+    return SPX_OK;
+}
+
 // Shrinks a persistent grid so that every group runs the same number of row iterations
 // (a grid of 9324 groups over 16384 rows would give some groups two rows and others one).
 static int balanced_blocks(uint64_t rows, int groups_per_block, int max_blocks)
@@ -260,49 +344,59 @@ static int balanced_blocks(uint64_t rows, int groups_per_block, int max_blocks)
     return (int)(blocks ? blocks : 1);
 }
 
+// Small x (up to 32 KB): the pipelined kernel on a grid with the same number of CTAs on every SM.
+template <int LPR>
+int launch_small(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s)
+{
+    const int sms = spx::sm_count(e->device);
+    const size_t xbytes = (size_t)e->n * sizeof(float);
+    const uint64_t groups_needed = e->m;
+    // Rows of near-equal length need no schedule: slot == row saves one dependent load per row.
+    const uint32_t* order = (e->max_nnz - e->min_nnz) * 8u <= e->max_nnz ? nullptr : e->row_order;
+    // Rows per group (iters) as if every SM held 4 CTAs of 512 threads; then the same number of CTAs
+    // on every SM -- as few as carry the rows in that many iterations (x is staged once per CTA) --
+    // each with equally many groups.  A grid that is not a multiple of the SM count leaves some SMs
+    // with one CTA more than others for the whole kernel.
+    constexpr int kPerSm = 4, kThreadsFull = 512;
+    const uint64_t cap = (uint64_t)sms * kPerSm * (kThreadsFull / LPR);
+    const uint64_t iters = (groups_needed + cap - 1) / cap;
+    const uint64_t per_iter = (groups_needed + iters - 1) / iters;         // groups that must exist
+    int threads = kThreadsFull, blocks = sms * kPerSm;
+    for (int k = 1; k <= kPerSm; ++k) {
+        const uint64_t g = (per_iter + (uint64_t)sms * k - 1) / ((uint64_t)sms * k);
+        const uint64_t t = (g * LPR + 31) / 32 * 32;
+        if (t <= std::min<uint64_t>(1024, 2048 / k)) {
+            threads = (int)t;
+            blocks = (int)std::min<uint64_t>((uint64_t)sms * k, (per_iter + g - 1) / g);
+            break;
+        }
+    }
+    spmv_ell_small_kernel<LPR><<<blocks, threads, xbytes, s>>>(e->Wd, e->idx, e->nnz, order, e->m, e->n, e->pitch, x, bias, y);
+    SPX_LAUNCH_CHECK("spmv_ell_small_kernel");
+    return SPX_OK;
+}
+
 template <int LPR>
 int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s)
 {
     const int sms = spx::sm_count(e->device);
     const size_t xbytes = (size_t)e->n * sizeof(float);
+    // Measured on B200: the pipelined kernel wins for 4096 columns at every sparsity (8.7 -> 8.1 us
+    // at 90 %, 12 -> 10.4 us at 80 %); at 16384 columns it is mixed and with x gathered from global
+    // memory it is 6 % slower, so larger matrices keep the kernel below.
+    if (xbytes <= kSmallX) return launch_small<LPR>(e, x, bias, y, s);
     const size_t kSmemMax = 200 * 1024;      // leaves room for a second small CTA's static needs
     const uint64_t groups_needed = e->m;
-    // Rows of near-equal length need no schedule: slot == row saves one dependent load per row.
-    const uint32_t* order = (e->max_nnz - e->min_nnz) * 8u <= e->max_nnz ? nullptr : e->row_order;
     if (xbytes <= kSmemMax) {
         // CTAs per SM limited by the staged copy of x; 2048 threads per SM at most.
         int per_sm = (int)((220 * 1024) / (xbytes + 1024));
         if (per_sm < 1) per_sm = 1;
         if (per_sm > 4) per_sm = 4;
-        // Rows per group (iters) as if every SM held per_sm CTAs of full size; then the same number of
-        // CTAs on every SM -- as few as carry the rows in that many iterations (x is staged once per
-        // CTA) -- each with equally many groups.  A grid that is not a multiple of the SM count
-        // leaves some SMs with one CTA more than others for the whole kernel.
-        int threads_full = 2048 / per_sm;
-        if (threads_full > 1024) threads_full = 1024;
-        threads_full &= ~31;
-        const uint64_t cap = (uint64_t)sms * per_sm * (threads_full / LPR);
-        const uint64_t iters = (groups_needed + cap - 1) / cap;
-        const uint64_t per_iter = (groups_needed + iters - 1) / iters;         // groups that must exist
-        int threads = threads_full, blocks = sms * per_sm;
-        for (int k = 1; k <= per_sm; ++k) {
-            const uint64_t g = (per_iter + (uint64_t)sms * k - 1) / ((uint64_t)sms * k);
-            const uint64_t t = (g * LPR + 31) / 32 * 32;
-            const uint64_t tmax = std::min<uint64_t>(1024, 2048 / k);
-            if (t <= tmax) {
-                threads = (int)t;
-                blocks = (int)std::min<uint64_t>((uint64_t)sms * k, (per_iter + g - 1) / g);
-                break;
-            }
-        }
-        auto kfn = spmv_ell_kernel<LPR, true>;
-        if (xbytes > 48 * 1024) {
-            cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xbytes);
-            if (err != cudaSuccess) return spx::fail(SPX_ERR_CUDA, "spmv: shared memory opt-in failed: %s", cudaGetErrorString(err));
-        }
-        kfn<<<blocks, threads, xbytes, s>>>(e->Wd, e->idx, e->nnz, order, e->m, e->n, e->pitch, x, bias, y);
-        SPX_LAUNCH_CHECK("spmv_ell_kernel");
-        return SPX_OK;
+        int threads = 2048 / per_sm;
+        if (threads > 1024) threads = 1024;
+        threads &= ~31;
+        const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * per_sm);
+        return launch_one<LPR, true>(e, x, bias, y, s, threads, blocks, xbytes);
     }
     if (e->spmv_split) {
         const int blocks = balanced_blocks(groups_needed, 1024 / LPR, sms);
@@ -317,9 +411,7 @@ int launch_lpr(const spx_ell* e, const float* x, const float* bias, float* y, cu
     }
     int threads = 512;
     const int blocks = balanced_blocks(groups_needed, threads / LPR, sms * 4);
-    spmv_ell_kernel<LPR, false><<<blocks, threads, 0, s>>>(e->Wd, e->idx, e->nnz, order, e->m, e->n, e->pitch, x, bias, y);
-    SPX_LAUNCH_CHECK("spmv_ell_kernel");
-    return SPX_OK;
+    return launch_one<LPR, false>(e, x, bias, y, s, threads, blocks, 0);
 }
 
 }  // namespace

@@ -173,6 +173,21 @@ def test_config5_headline_shape_vs_oracle(lib, orc, cuda):
         assert_bit_equal(out.cpu().numpy(), got[g * half:(g + 1) * half], f"half shard {g}")
 
 
+@pytest.mark.parametrize("env", [{"SPX_SPMM_STAGED": "0"}, {"SPX_SPMM_STAGED": "1"}], ids=["gather_vec", "gather_staged"])
+def test_spmm_each_wide_kernel_forced(env):
+    """Wide X with long rows runs on one of two kernels, chosen by an estimate of whether the longest
+    row's chain decides the duration; the switch is read once per process, so each kernel is forced
+    in a child process that reruns the SpMM parity cases with long rows (among them the headline
+    shape: n = 65536, C = 1024, four panels, the 2048-entry row)."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+           os.path.join(here, "test_parity_gpu.py"), "-k", "long_rows_several_panels or headline_shape or config5_shard"]
+    r = subprocess.run(cmd, env={**os.environ, **env}, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
 @pytest.mark.parametrize("act", [sx.ACT_SIGMOID, sx.ACT_TANH])
 def test_spmm_sigmoid_tanh_epilogue(lib, orc, cuda, act):
     rng = np.random.default_rng(act)
