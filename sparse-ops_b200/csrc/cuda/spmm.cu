@@ -162,7 +162,9 @@ struct StagedMap {
     uint32_t row_blocks;    // row blocks (one row per warp)
     uint32_t head;          // row blocks on the narrow path, issued first, panel-minor
     uint32_t head_panels;   // 128-column panels
-    uint32_t panels;        // 256-column panels of the wide path
+    uint32_t panels;        // panels of the other row blocks: 256 columns, or 128 when all_narrow
+    uint32_t all_narrow;    // every row on 128-column panels (panel-major, so one 128-column panel of X is in use at a time)
+    uint32_t rest_ascending;    // the rows behind the head run shortest first (see launch_spmm_bcast)
 };
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
@@ -274,15 +276,19 @@ spmm_gather_staged(const float* __restrict__ Wd, const uint32_t* __restrict__ id
         panel = t / rest;
         rb = sm.head + t % rest;
     }
-    const uint32_t slot = rb * (blockDim.x >> 5) + warp;
+    uint32_t slot = rb * (blockDim.x >> 5) + warp;
     if (slot >= m) return;                      // whole warp leaves together
+    if (!narrow && sm.rest_ascending) {
+        const uint32_t first = sm.head * (blockDim.x >> 5);      // schedule slots [first, m) in reverse
+        slot = first + (m - 1 - slot);
+    }
     const uint32_t row = __ldg(row_order + slot);
     const float b = bias ? __ldg(bias + row) : 0.0f;
     const uint32_t nn = __ldg(nnz + row);
     const float* __restrict__ w = Wd + (size_t)row * pitch;
     const uint32_t* __restrict__ k = idx + (size_t)row * pitch;
     const size_t out_row = (size_t)(out.row0 + row) * ldy;
-    if (narrow) {
+    if (narrow || sm.all_narrow) {
         const uint32_t c0 = panel * 128u + 4u * lane;
         staged_row<1, 8>(w, k, nn, X, c0, C, ldxb, b, act, out, out_row + c0, s_w, s_k, lane);
     } else {
@@ -582,10 +588,18 @@ static BlockMap block_map(const spx_ell* e, uint32_t C, uint32_t panels, uint32_
 // Measured on B200 (power-law rows, mean 64, max 2048, n = 65536, C = 1024), staged kernel against
 // spmm_gather_vec: 32768 rows 0.556 against 0.610 ms, 65536 rows 1.00 against 1.00 ms, 262144 rows
 // 4.21 against 4.09 ms.  SPX_SPMM_STAGED=0|1 overrides.
-static bool chain_bound(const spx_ell* e, uint32_t C)
+static int staged_mode()
 {
     static const int forced = [] { const char* v = getenv("SPX_SPMM_STAGED"); return v ? atoi(v) : -1; }();
-    if (e->long_rows == 0 || C <= 128) return false;
+    return forced;
+}
+
+static bool chain_bound(const spx_ell* e, uint32_t C)
+{
+    const int forced = staged_mode();
+    if (C <= 128) return false;
+    if (forced == 2) return true;                   // experiment: every row on 128-column panels
+    if (e->long_rows == 0) return false;
     if (forced >= 0) return forced != 0;
     const double kernel_us = (double)e->nnz_total * C * 4.0 / 17e6 * (148.0 / sm_count(e->device));
     const double chain_us = e->max_nnz / 4.0 * 1.2;
@@ -657,12 +671,20 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
         // gives the rows with 512 and more entries 128-column panels with eight rows of X in
         // flight per round trip (half the round trips), issued first.
         if (nv == 2 && ldx < (1ull << 30) && chain_bound(e, C)) {
+            const bool all_narrow = staged_mode() == 2;
             const uint32_t wpb = gather_wpb(e, (C + 255) / 256);
             StagedMap sm{};
+            sm.all_narrow = all_narrow ? 1u : 0u;
+            // With the exchange fused in, every finished row is 4*C bytes to each peer, whatever its
+            // length.  In descending order the many short rows all finish at the end and the links
+            // idle until then; shortest first behind the head keeps them busy from the start, while
+            // the long rows (the head) still start at once.  SPX_SPMM_BCAST_ORDER=0 keeps descending.
+            static const int order_env = [] { const char* v = getenv("SPX_SPMM_BCAST_ORDER"); return v ? atoi(v) : 1; }();
+            sm.rest_ascending = (npeers > 1 && order_env) ? 1u : 0u;
             sm.row_blocks = (e->m + wpb - 1) / wpb;
-            sm.panels = (C + 255) / 256;
+            sm.panels = all_narrow ? (C + 127) / 128 : (C + 255) / 256;
             sm.head_panels = (C + 127) / 128;
-            sm.head = std::min<uint32_t>(sm.row_blocks, (e->long_rows + wpb - 1) / wpb);
+            sm.head = all_narrow ? 0u : std::min<uint32_t>(sm.row_blocks, (e->long_rows + wpb - 1) / wpb);
             sm.blocks = sm.head * sm.head_panels + (sm.row_blocks - sm.head) * sm.panels;
             spmm_gather_staged<<<sm.blocks, wpb * 32, (size_t)wpb * 512, s>>>(e->Wd, e->idx, e->nnz, e->row_order, e->m, e->pitch,
                                                                           X, C, (uint32_t)(ldx * 4), bias, act, out, ldy, sm);

@@ -97,6 +97,32 @@ def main():
     lib.spx_memcpy_d2h(got.ctypes.data_as(C.c_void_p), buf, nbytes, 0)
     lib.spx_device_sync()
     assert np.array_equal(got[:m].view(np.uint32), want.view(np.uint32)), "fused SpMM + all-gather differs"
+    # 1c. the same fused exchange on a skewed matrix (rows of 512 and more entries, wide X): the
+    # staged kernel, long rows first, the others shortest first; the exchange buffers of 1b are reused
+    m2, n2 = 2 * 301, 1200
+    W2 = sparse(rng, m2, n2, 0.02)
+    for row, cnt in ((5, 600), (310, 1200), (601, 513)):
+        W2[row] = 0
+        W2[row, rng.choice(n2, cnt, replace=False)] = rng.standard_normal(cnt).astype(np.float32)
+    Cw = 132                                         # > 128: the wide kernels
+    X2 = rng.uniform(-1, 1, (n2, Cw)).astype(np.float32)
+    b2 = rng.standard_normal(m2).astype(np.float32)
+    assert m2 * Cw * 4 <= nbytes
+    per2 = -(-m2 // world)
+    lo2 = min(m2, rank * per2)
+    S2 = sb.encode_host(W2).shard_rows(rank, world, upload=False)
+    h2 = lib.ell_create(S2.Wd, S2.idx, S2.nnz, n2)
+    dX2 = torch.from_numpy(X2).to(dev)
+    dB2 = torch.from_numpy(b2[lo2:lo2 + S2.m].copy()).to(dev)
+    dist.barrier()
+    lib.spx_spmm_bcast(h2.h, dX2.data_ptr(), Cw, Cw, dB2.data_ptr(), sx.ACT_NONE, arr, world, rank * per2, Cw, stream)
+    lib.spx_comm_barrier(comm, stream)
+    torch.cuda.synchronize()
+    got2 = np.empty((per2 * world, Cw), np.float32)
+    lib.spx_memcpy_d2h(got2.ctypes.data_as(C.c_void_p), buf, got2.nbytes, 0)
+    lib.spx_device_sync()
+    want2 = orc.spmm(orc.encode(W2), X2, b2)
+    assert np.array_equal(got2[:m2].view(np.uint32), want2.view(np.uint32)), "fused exchange on a skewed matrix differs"
     dist.barrier()
     for pp in opened:
         lib.spx_ipc_close(pp)

@@ -173,6 +173,36 @@ def test_config5_headline_shape_vs_oracle(lib, orc, cuda):
         assert_bit_equal(out.cpu().numpy(), got[g * half:(g + 1) * half], f"half shard {g}")
 
 
+@pytest.mark.parametrize("C", [64, 260, 1024])
+def test_spmm_bcast_into_two_buffers_long_rows(lib, orc, cuda, C):
+    """The SpMM whose epilogue stores every finished row into several full-size buffers (the fused
+    exchange of the row-sharded path), here with two buffers on one GPU, a row offset, and rows of
+    512 and more entries: with more than one destination the rows behind the long ones run shortest
+    first.  Both buffers against the oracle, bit for bit; rows outside the shard stay untouched."""
+    import ctypes as Ct
+    m, n, row0, total = 1500, 3000, 200, 2000
+    rng = np.random.default_rng([C, 77])
+    W = sparse(rng, m, n, 0.01)
+    for row, cnt in ((0, 700), (1, 513), (600, 3000), (1499, 1024)):
+        W[row] = 0
+        cols = rng.choice(n, cnt, replace=False)
+        W[row, cols] = rng.standard_normal(cnt).astype(np.float32)
+    X = rng.uniform(-1, 1, (n, C)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    dX, dB = dev(X, cuda), dev(b, cuda)
+    bufs = [torch.full((total, C), float("nan"), device=cuda, dtype=torch.float32) for _ in range(2)]
+    arr = (Ct.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    lib.spx_spmm_bcast(h.h, dX.data_ptr(), C, C, dB.data_ptr(), sx.ACT_RELU, arr, 2, row0, C, 0)
+    torch.cuda.synchronize()
+    want = orc.spmm(E, X, b, act=1)
+    for i, buf in enumerate(bufs):
+        got = buf.cpu().numpy()
+        assert_bit_equal(got[row0:row0 + m], want, f"buffer {i}")
+        assert np.isnan(got[:row0]).all() and np.isnan(got[row0 + m:]).all()
+
+
 @pytest.mark.parametrize("env", [{"SPX_SPMM_STAGED": "0"}, {"SPX_SPMM_STAGED": "1"}], ids=["gather_vec", "gather_staged"])
 def test_spmm_each_wide_kernel_forced(env):
     """Wide X with long rows runs on one of two kernels, chosen by an estimate of whether the longest
@@ -183,7 +213,7 @@ def test_spmm_each_wide_kernel_forced(env):
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
-           os.path.join(here, "test_parity_gpu.py"), "-k", "long_rows_several_panels or headline_shape or config5_shard"]
+           os.path.join(here, "test_parity_gpu.py"), "-k", "long_rows_several_panels or headline_shape or config5_shard or bcast_into_two_buffers"]
     r = subprocess.run(cmd, env={**os.environ, **env}, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
