@@ -166,7 +166,8 @@ int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float
  * stream capture.  The CUDA runtime places the library's device code, and with it the 4 MiB
  * array, on a GPU when the library is first used there: make one warm-up call per device (or any
  * other call into this library) at start-up, before the host's own pool claims the remaining
- * memory.  Same arguments and results as spx_conv2d. */
+ * memory.  Same arguments and results as spx_conv2d, for the layouts SPX_LAYOUT_PF and
+ * SPX_LAYOUT_NCHW (the F-major layout needs scratch tensors and is refused with SPX_ERR_ARG). */
 int spx_conv2d_static(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                       const float* bias, int act, float* out, void* stream);
 /* out = op(a[, b]) elementwise; replaces applyRelu/Sigmoid/Tanh (src/layers/activation.cpp:3-62),
@@ -214,7 +215,7 @@ int spx_comm_info(const spx_comm* c, int* rank, int* world);      /* either poin
  * phase_ms (may be NULL): four floats, the device time this rank spent in the copy in, the
  * exchange, the multiply and the copy out, summed over the panels (the stages overlap, so their
  * sum exceeds the call's duration).  comm == NULL or a world of 1: same as spx_spmm_host.
- * Synchronous.  Up to 2048 columns. */
+ * Synchronous.  Up to 1792 columns. */
 int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* e, const float* X, uint32_t C, const float* bias,
                           int act, float* Y, float* phase_ms);
 

@@ -533,6 +533,19 @@ int spx_eltwise(int op, const float* a, const float* b, float* out, uint64_t cou
     return launch_eltwise(op, a, b, out, count, (cudaStream_t)stream);
 }
 
+// Column panels of the pipelined host-buffer SpMM: 256 columns, except that a wide operand starts
+// with a panel of 64 (then 192, back on the 256 grid): the first copy out can only begin after
+// the first panel has been copied in and multiplied, and that lead time is not overlapped with
+// anything, so the first panel is kept small.
+static inline uint32_t host_panel_width(uint32_t c0, uint32_t C)
+{
+    if (C >= 512) {
+        if (c0 == 0) return 64;
+        if (c0 == 64) return 192;
+    }
+    return std::min<uint32_t>(256, C - c0);
+}
+
 // ---- host-buffer entry points ----------------------------------------------------------------
 // Pageable host buffers are copied by the driver through its own pinned bounce buffers; callers
 // that pass pinned memory (spx_host_alloc) get direct DMA.  Layout of the staging block:
@@ -566,8 +579,8 @@ int spx_spmm_host(const spx_ell* ce, const float* X, uint32_t C, const float* bi
         cudaEvent_t ev_in = e->pipe_events[0], ev_mm = e->pipe_events[1];
         cudaError_t err = cudaSuccess;
         if (bias) err = cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, s_in);
-        for (uint32_t c0 = 0; c0 < C && err == cudaSuccess && rc == SPX_OK; c0 += 256) {
-            const uint32_t w = std::min<uint32_t>(256, C - c0);
+        for (uint32_t c0 = 0, w = 0; c0 < C && err == cudaSuccess && rc == SPX_OK; c0 += w) {
+            w = host_panel_width(c0, C);
             err = cudaMemcpy2DAsync(dX + c0, (size_t)C * 4, X + c0, (size_t)C * 4, (size_t)w * 4, e->n, cudaMemcpyHostToDevice, s_in);
             if (err == cudaSuccess) err = cudaEventRecord(ev_in, s_in);
             if (err == cudaSuccess) err = cudaStreamWaitEvent(s_mm, ev_in, 0);
@@ -615,10 +628,10 @@ int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* ce, const float* X, uin
     if (C == 0) return SPX_OK;                       // nothing to exchange either: every rank returns here
     if ((!Y && e->m) || (!X && e->n)) return fail(SPX_ERR_ARG, "X / Y is null");
     DeviceGuard g(e->device);
-    constexpr uint32_t kPanel = 256;
-    const uint32_t panels = (C + kPanel - 1) / kPanel;
+    uint32_t panels = 0;
+    for (uint32_t c0 = 0; c0 < C; c0 += host_panel_width(c0, C)) ++panels;
     constexpr uint32_t kMaxPanels = sizeof(e->pipe_events) / sizeof(e->pipe_events[0]) / 8;    // 2 events x 4 stages each
-    if (panels > kMaxPanels) return fail(SPX_ERR_LIMIT, "spmm_host_sharded: C beyond %u columns", kMaxPanels * kPanel);
+    if (panels > kMaxPanels) return fail(SPX_ERR_LIMIT, "spmm_host_sharded: C beyond %u columns", (kMaxPanels - 1) * 256);
     const uint64_t per = ((uint64_t)e->n + world - 1) / world;       // rows of X per rank (last block may be short)
     const uint64_t lo = std::min<uint64_t>(e->n, per * rank), hi = std::min<uint64_t>(e->n, lo + per);
     const size_t xb = round_up<size_t>((size_t)per * world * C * 4, 256);
@@ -639,8 +652,8 @@ int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* ce, const float* X, uin
 
     cudaError_t err = cudaSuccess;
     if (bias && e->m) err = cudaMemcpyAsync(dB, bias, (size_t)e->m * 4, cudaMemcpyHostToDevice, st[0]);
-    for (uint32_t p = 0; p < panels && err == cudaSuccess && rc == SPX_OK; ++p) {
-        const uint32_t c0 = p * kPanel, w = std::min<uint32_t>(kPanel, C - c0);
+    for (uint32_t p = 0, c0 = 0, w = 0; p < panels && err == cudaSuccess && rc == SPX_OK; ++p, c0 += w) {
+        w = host_panel_width(c0, C);
         float* dXp = dX + (size_t)per * world * c0;                   // panel p: [per * world x w], contiguous
         // 0: this rank's rows of the panel, host -> device
         err = cudaEventRecord(ev(p, 0, 0), st[0]);
