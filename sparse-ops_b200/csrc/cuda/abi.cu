@@ -643,8 +643,13 @@ int spx_spmm_host_sharded(spx_comm* comm, const spx_ell* ce, const float* X, uin
     float* dX = reinterpret_cast<float*>(base);
     float* dB = reinterpret_cast<float*>(base + xb);
     float* dY = reinterpret_cast<float*>(base + xb + bb);
-    for (cudaStream_t& st : e->pipe_streams)
-        if (!st) SPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    // The exchange stream gets the highest priority: the all-gather of panel p+1 runs next to the
+    // multiply of panel p, and its few CTAs must not queue behind the multiply's thousands.
+    int prio_lo = 0, prio_hi = 0;
+    SPX_CUDA(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
+    for (int i = 0; i < 4; ++i)
+        if (!e->pipe_streams[i])
+            SPX_CUDA(cudaStreamCreateWithPriority(&e->pipe_streams[i], cudaStreamNonBlocking, i == 1 ? prio_hi : prio_lo));
     for (uint32_t i = 0; i < panels * 8; ++i)
         if (!e->pipe_events[i]) SPX_CUDA(cudaEventCreate(&e->pipe_events[i]));
     cudaStream_t st[4] = {e->pipe_streams[0], e->pipe_streams[1], e->pipe_streams[2], e->pipe_streams[3]};

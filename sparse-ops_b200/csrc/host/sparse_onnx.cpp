@@ -32,6 +32,10 @@ struct SparseOnnxModel::Exec {
     std::unordered_map<std::string, uint64_t> rows;   // tensor name -> rows (elements per column)
     std::vector<void*> owned;
     size_t distinct_buffers = 0;       // activation buffers actually allocated (fewer than tensors when reused)
+    // Small results leave the device through a pinned staging buffer: a device -> host copy into
+    // the caller's pageable array goes through the driver's bounce buffer in serialised chunks.
+    float* h_out = nullptr;
+    size_t h_out_bytes = 0;
     // Row-sharded mode with the exchange fused into the SpMM epilogue: for every MatMul output the
     // full buffer of each rank (own pointer + peers' buffers opened over IPC), indexed by rank.
     bool fused = false;
@@ -47,6 +51,7 @@ struct SparseOnnxModel::Exec {
         }
         for (void* p : owned) spx_free(p);
         spx_free(d_bias);
+        spx_host_free(h_out);
         if (stream) spx_stream_destroy(stream);
     }
 };
@@ -452,6 +457,10 @@ void SparseOnnxModel::build_exec(uint32_t B) const
             }
     }
     ex->distinct_buffers = ex->owned.size();
+    const size_t out_bytes = size_t(out_features_) * B * sizeof(float);
+    if (out_bytes && out_bytes <= (size_t(8) << 20) &&
+        spx_host_alloc(reinterpret_cast<void**>(&ex->h_out), out_bytes) == SPX_OK)
+        ex->h_out_bytes = out_bytes;        // without it run() copies straight into the caller's array
     if (world_ > 1 && comm_) {
         ex->comm = comm_;
         const char* off = std::getenv("SPX_TP_FUSED");
@@ -570,7 +579,14 @@ void SparseOnnxModel::run(const float* input, uint32_t B, float* output) const
     check(spx_memcpy_h2d(d_in, input, size_t(in_features_) * B * sizeof(float), ex.stream), "input copy");
     if (ex.graph) check(spx_graph_launch(ex.graph, ex.stream), "graph launch");
     else launch_layers(d_in, d_out, B, ex.stream);
-    check(spx_memcpy_d2h(output, d_out, size_t(out_features_) * B * sizeof(float), ex.stream), "output copy");
+    const size_t out_bytes = size_t(out_features_) * B * sizeof(float);
+    if (ex.h_out && ex.h_out_bytes == out_bytes) {
+        check(spx_memcpy_d2h(ex.h_out, d_out, out_bytes, ex.stream), "output copy");
+        check(spx_stream_sync(ex.stream), "run");
+        std::memcpy(output, ex.h_out, out_bytes);
+        return;
+    }
+    check(spx_memcpy_d2h(output, d_out, out_bytes, ex.stream), "output copy");
     check(spx_stream_sync(ex.stream), "run");
 }
 
