@@ -486,6 +486,26 @@ def test_host_buffer_entry_points(lib, orc, cuda):
     assert lib.spx_launch_count() == before + 1
 
 
+def test_sharded_host_entry_point_without_a_communicator(lib, orc, cuda):
+    """spx_spmm_host_sharded with no communicator (one process, one GPU) is spx_spmm_host: same
+    bytes out, stage times reported as zero."""
+    import ctypes as C
+    rng = np.random.default_rng(29)
+    W = sparse(rng, 300, 200, 0.1)
+    X = rng.uniform(-1, 1, (200, 40)).astype(np.float32)
+    b = rng.standard_normal(300).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    Y = np.full((300, 40), np.nan, np.float32)
+    phases = (C.c_float * 4)(1, 1, 1, 1)
+    fp = lambda a: a.ctypes.data_as(C.c_void_p)
+    lib.spx_spmm_host_sharded(None, h.h, fp(X), 40, fp(b), sx.ACT_RELU, fp(Y), phases)
+    assert_bit_equal(Y, orc.spmm(E, X, b, act=1), "sharded entry point, world of one")
+    assert list(phases) == [0.0, 0.0, 0.0, 0.0]
+    with pytest.raises(sx.SpxError):
+        lib.spx_spmm_host_sharded(None, None, fp(X), 40, fp(b), sx.ACT_RELU, fp(Y), None)
+
+
 def test_config1_scaled_and_linearity(lib, orc, cuda):
     """Config 1 recipe at reduced size: oracle parity, plus linearity at the full size where the
     oracle would take too long for a unit test: E(aX1 + X2) == a E X1 + E X2 within rounding."""
