@@ -10,8 +10,8 @@ input.  Workloads (the five benchmark configurations):
                         the largest single-GPU SpMM configuration.  N > 1: rows of E split over
                         the ranks, X replicated, Y stays row-sharded (strong scaling, no
                         collective in `value`); the NCCL all-gather of Y is timed separately.
-  cfg1_spmm / cfg1_spmv 4096^2, p = 0.1 (C = 256 for SpMM).  Fits in L2, so L2 is flushed
-                        between timed iterations.
+  cfg1_spmm / cfg1_spmv 4096^2, p = 0.1 (C = 256 for SpMM).  Fits in L2, so the operands are
+                        replicated and the launches rotate through the copies.
   cfg2_spmv             square iid matrix, --size in {4096,16384,65536}, --sparsity.
   cfg3_mlp              sparse MLP 4096-4096-4096-4096-1000, batch 256, via SparseOnnxModel
                         (N > 1: batch-sharded, no collective; --tp: row-sharded + all-gather).
@@ -19,9 +19,13 @@ input.  Workloads (the five benchmark configurations):
   cfg4_stack            four such layers chained, through SparseOnnxModel.
 
 `value` is measured with operands resident in HBM; `e2e` is the same metric through the
-host-buffer entry points (pinned host memory, copies inside the timed region).
+host-buffer entry points (pinned host memory, copies inside the timed region; at N > 1 every rank
+copies its block of X, the ranks rebuild X over NVLink, and each copies its own rows of Y back).
+After the timed regions sampled rows of every result buffer are compared with the CPU oracle on
+every rank (`check`); a mismatch makes the run fail.  The default run also carries the other
+configurations under `also` (N = 1: configs 1 - 4; N > 1: the MLP batch- and row-sharded).
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, else the C port)
-on a bounded sample of the same workload.
+on the whole matrix per step where the host's memory holds it.
 """
 from __future__ import annotations
 
