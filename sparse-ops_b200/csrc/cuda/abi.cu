@@ -395,6 +395,8 @@ int spx_ell_destroy(spx_ell* e)
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
     cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch); cudaFree(e->fm_scratch);
+    if (e->tma_failed_host) cudaFreeHost(e->tma_failed_host);
+    if (e->tma_failed_dev) cudaFree(e->tma_failed_dev);
     for (cudaStream_t st : e->pipe_streams) if (st) cudaStreamDestroy(st);
     for (cudaEvent_t ev : e->pipe_events) if (ev) cudaEventDestroy(ev);
     delete e;

@@ -44,6 +44,13 @@ struct spx_ell {
     float* rbm_w = nullptr;
     uint32_t* rbm_ncols = nullptr;
     uint32_t rbm_cap = 0, rbm_kH = 0, rbm_kW = 0;
+    // Raised by a convolution kernel whose bounded wait for a bulk tensor copy ran out: a word in
+    // device memory (read by the kernel's later CTAs) and a word in pinned host memory (its device
+    // alias is tma_failed_mapped; read by the next convolution call on the handle).
+    int* tma_failed_host = nullptr;
+    int* tma_failed_mapped = nullptr;
+    int* tma_failed_dev = nullptr;
+    bool tma_off = false;
     // SpMV with x larger than shared memory (spmv.cu): column window width and the per-row split
     // table, built on the first spx_spmv of such a handle.  spmv_win == UINT32_MAX: not applicable.
     uint32_t* spmv_split = nullptr;

@@ -14,11 +14,15 @@
 // kernel implements the mathematically correct stride).
 #include "common.cuh"
 
+#include <cuda.h>            // CUtensorMap and its enums only; the encoder is looked up at run time
+#include <cudaTypedefs.h>
+
 #include <algorithm>
 #include <climits>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -194,6 +198,7 @@ struct TileParams {
     uint32_t CC;        // input channels per staged chunk
     uint32_t THin, TWin;
     uint32_t tilesX;
+    uint32_t stage;     // floats between the two staging buffers of the bulk-copy path (0: one buffer)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -201,6 +206,41 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// ---- bulk tensor copies (TMA) for the staged input patch -----------------------------------------
+// One thread asks the copy unit for the whole [channels][rows][columns][batch] box of a chunk; the
+// unit writes it into shared memory (zeros where the box leaves the image) and signals an mbarrier
+// with the byte count.  No multicast, the tensor map covers this GPU's own input tensor only.
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+                   "r"((uint32_t)__cvta_generic_to_shared(bar)) : "memory");
+}
+// Waits for the phase with the given parity; gives up one second (of the GPU's wall clock) after
+// its 256th unsuccessful poll and returns false, so a copy that never completes cannot hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
+    uint64_t t0 = 0;
+    for (uint32_t i = 1;; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(a), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 255u) == 0) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 1000000000ull) return false;
+        }
+    }
+}
 
 // Stages input channels [c0, c1) of a CTA's receptive field in shared memory as
 // [channel][row][column][BT batch entries]: one warp per (channel, row), 16-byte cp.async copies,
@@ -240,7 +280,7 @@ conv_pf_tile_kernel(const float* __restrict__ Wd, const uint32_t* __restrict__ t
                     const float* __restrict__ in, const float* __restrict__ bias, int act,
                     float* __restrict__ out)
 {
-    extern __shared__ __align__(16) float tile[];
+    extern __shared__ __align__(128) float tile[];
     const ConvParams& p = tp.c;
     const uint32_t BT = QB * 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -453,9 +493,11 @@ __global__ void __launch_bounds__(NB * 32, 1)
 conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w4,
                      const uint32_t* __restrict__ ncols, uint32_t cap, TileParams tp, RbmUnits un,
                      const float* __restrict__ in, const float* __restrict__ bias, int act,
-                     float* __restrict__ out)
+                     float* __restrict__ out, const __grid_constant__ CUtensorMap tmap, uint32_t use_tma,
+                     int* __restrict__ tma_failed, int* __restrict__ tma_failed_host)
 {
-    extern __shared__ __align__(16) float tile[];
+    extern __shared__ __align__(128) float tile[];
+    __shared__ __align__(8) uint64_t tile_bar[2];
     constexpr int RB = (int)kRbmRows;
     constexpr uint32_t BT = QB * 4;
     constexpr uint32_t TH = 32u * G / QB / kTileW;       // rows of output positions per tile
@@ -492,10 +534,47 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
     const uint2* __restrict__ hrow = hdr + (size_t)(active ? blk : 0) * cap;
     const float4* __restrict__ wrow = w4 + (size_t)(active ? blk : 0) * cap;
     uint32_t pos = 0;
+    // Bulk-copy staging: two buffers of tp.CC channels each.  Thread 0 asks the copy unit for the
+    // next chunk's box before the CTA starts on the current one, so the fetch overlaps the
+    // arithmetic; the unit writes shared memory itself (no load / store slots of the 16 warps) and
+    // fills the halo with zeros.  A box always has tp.CC channels; past the last channel it reads
+    // zeros.  Every wait is bounded: after a wait that ran out the CTA stops waiting, finishes on
+    // whatever the buffers hold, raises *tma_failed (the host then reports the call as failed) and
+    // CTAs that start later leave at once.
+    const uint32_t box_bytes = tp.CC * tp.THin * tp.TWin * BT * (uint32_t)sizeof(float);
+    bool landed = true;
+    if (use_tma) {
+        if (threadIdx.x == 0) {
+            mbar_init(&tile_bar[0], 1);
+            mbar_init(&tile_bar[1], 1);
+        }
+        if (__syncthreads_or(*reinterpret_cast<volatile int*>(tma_failed) != 0)) return;
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(&tile_bar[0], box_bytes);
+            tma_load_4d(tile, &tmap, (int)b0, iw0, ih0, 0, &tile_bar[0]);
+        }
+    }
+    uint32_t issued = 1;        // copies thread 0 has asked for
 
-    for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC) {
+    uint32_t chunk = 0;
+    for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC, ++chunk) {
         const uint32_t c1 = min(p.Cin, c0 + tp.CC);
-        stage_chunk<QB, NB>(tile, tp, in, c0, c1, ih0, iw0, b0, warp, lane);
+        const float* cur = tile;
+        if (use_tma) {
+            const uint32_t nb = (chunk + 1) & 1u;
+            if (threadIdx.x == 0 && c1 < p.Cin && landed) {
+                // buffer nb was last read for chunk - 1; the barrier that ended that chunk ordered
+                // those reads before this point, the fence orders them before the unit's writes
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(&tile_bar[nb], box_bytes);
+                tma_load_4d(tile + nb * tp.stage, &tmap, (int)b0, iw0, ih0, (int)c1, &tile_bar[nb]);
+                ++issued;
+            }
+            if (landed) landed = mbar_wait(&tile_bar[chunk & 1u], (chunk >> 1) & 1u);
+            cur = tile + (chunk & 1u) * tp.stage;
+        } else {
+            stage_chunk<QB, NB>(tile, tp, in, c0, c1, ih0, iw0, b0, warp, lane);
+        }
         if (active) {
             for (;;) {
                 // lane l preloads union column pos + l: shared-memory offset << 8 | row mask, and its 4 weights
@@ -511,7 +590,7 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
                 const uint32_t cnt = __popc(__ballot_sync(0xffffffffu, cin < c1));   // a prefix: columns ascend
                 for (uint32_t t = 0; t < cnt; ++t) {
                     const uint32_t hm = __shfl_sync(0xffffffffu, hl, t);
-                    const float* xs = tile + (hm >> 8);
+                    const float* xs = cur + (hm >> 8);
                     float4 x[G];
 #pragma unroll
                     for (int g = 0; g < G; ++g) x[g] = *reinterpret_cast<const float4*>(xs + off[g]);
@@ -525,6 +604,15 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
             }
         }
         __syncthreads();
+    }
+    if (use_tma && !landed) {
+        *tma_failed = 1;
+        *tma_failed_host = 1;
+        // the last two copies asked for may still be writing this CTA's shared memory: one more
+        // bounded wait for each before the CTA gives the memory up
+        if (threadIdx.x == 0)
+            for (uint32_t j = issued > 2 ? issued - 2 : 0; j < issued; ++j)
+                (void)mbar_wait(&tile_bar[j & 1u], (j >> 1) & 1u);
     }
     if (!active) return;
 #pragma unroll
@@ -622,6 +710,21 @@ static int ensure_rbm(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
             return -1;
         }
         e->rbm_cap = cap;
+        // Two words for a kernel whose bounded wait for a bulk tensor copy runs out: one in device
+        // memory, which CTAs that start later read and leave on, and one in pinned host memory
+        // (only ever written by the kernel: a read of host memory costs an SM about a microsecond),
+        // which the next convolution call on the handle reports.
+        if (!e->tma_failed_host && cudaHostAlloc(reinterpret_cast<void**>(&e->tma_failed_host), sizeof(int), cudaHostAllocMapped) == cudaSuccess) {
+            *e->tma_failed_host = 0;
+            if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&e->tma_failed_mapped), e->tma_failed_host, 0) != cudaSuccess ||
+                cudaMalloc(reinterpret_cast<void**>(&e->tma_failed_dev), sizeof(int)) != cudaSuccess ||
+                cudaMemset(e->tma_failed_dev, 0, sizeof(int)) != cudaSuccess) {
+                e->tma_failed_mapped = nullptr;
+                if (e->tma_failed_dev) cudaFree(e->tma_failed_dev);
+                e->tma_failed_dev = nullptr;
+            }
+        }
+        (void)cudaGetLastError();
     }
     const size_t smem = (size_t)((e->n + 31) / 32) * 2 * sizeof(uint32_t);
     build_rbm_kernel<<<nblocks, 256, smem, s>>>(e->Wd, e->idx, e->nnz, e->m, e->n, e->pitch, kH, kW, e->rbm_cap,
@@ -630,6 +733,22 @@ static int ensure_rbm(spx_ell* e, uint32_t kH, uint32_t kW, cudaStream_t s)
     e->rbm_kH = kH;
     e->rbm_kW = kW;
     return SPX_OK;
+}
+
+// cuTensorMapEncodeTiled, looked up through the runtime (the library does not link libcuda).
+static PFN_cuTensorMapEncodeTiled tensor_map_encoder()
+{
+    static const PFN_cuTensorMapEncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            p = nullptr;
+        }
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+    }();
+    return fn;
 }
 
 template <int QB, int G>
@@ -645,12 +764,38 @@ static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32
     const size_t chanBytes = (size_t)tp.THin * tp.TWin * tp.BT * sizeof(float);
     const size_t budget = 200 * 1024;
     tp.CC = (uint32_t)std::min<size_t>(p.Cin, budget / chanBytes);
-    const size_t smem = chanBytes * tp.CC;
+    // The chunk's patch as one bulk tensor copy (TMA) where a map of the input tensor can be made:
+    // dimensions, innermost first, [B][W][H][Cin]; box [BT][TWin][THin][CC] (each extent at most
+    // 256); positions outside the tensor read as zero, which is the halo.  The innermost
+    // coordinate of every copy is a multiple of BT floats, i.e. of 16 bytes, as the copy unit
+    // requires.  SPX_CONV_TMA=0 keeps the per-thread cp.async staging.
+    static const int tma_env = [] { const char* v = getenv("SPX_CONV_TMA"); return v ? atoi(v) : 1; }();
+    CUtensorMap map;
+    std::memset(&map, 0, sizeof(map));
+    uint32_t use_tma = 0;
+    const PFN_cuTensorMapEncodeTiled encode = tensor_map_encoder();
+    if (tma_env && !e->tma_off && encode && e->tma_failed_dev && e->tma_failed_mapped && tp.TWin <= 256 && tp.THin <= 256 &&
+        p.B % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+        // two buffers: half the channels of the single-buffer chunk each
+        const uint32_t cc = std::min<uint32_t>(std::max<uint32_t>(1u, (uint32_t)(budget / 2 / chanBytes)), std::min<uint32_t>(p.Cin, 256));
+        const cuuint64_t gdim[4] = {p.B, p.W, p.H, p.Cin};
+        const cuuint64_t gstr[3] = {(cuuint64_t)p.B * 4, (cuuint64_t)p.W * p.B * 4, (cuuint64_t)p.H * p.W * p.B * 4};
+        const cuuint32_t box[4] = {tp.BT, tp.TWin, tp.THin, cc};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(in), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            use_tma = 1;
+            tp.CC = cc;
+            tp.stage = (uint32_t)((chanBytes * cc + 127) / 128 * 32);     // buffers start on 128-byte boundaries
+        }
+    }
+    const size_t smem = use_tma ? (size_t)tp.stage * (p.Cin > tp.CC ? 2 : 1) * sizeof(float) : chanBytes * tp.CC;
     auto kfn = conv_rbm_tile_kernel<QB, NB, G>;
     cudaError_t err = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return fail(SPX_ERR_CUDA, "conv2d: shared memory opt-in failed: %s", cudaGetErrorString(err));
     kfn<<<ctas, NB * 32, smem, s>>>(e->rbm_hdr, reinterpret_cast<const float4*>(e->rbm_w), e->rbm_ncols, e->rbm_cap,
-                                    tp, un, in, bias, act, out);
+                                    tp, un, in, bias, act, out, map, use_tma, e->tma_failed_dev, e->tma_failed_mapped);
     SPX_LAUNCH_CHECK("conv_rbm_tile_kernel");
     return SPX_OK;
 }
@@ -706,6 +851,12 @@ static int launch_conv_rbm_tile(spx_ell* e, const ConvParams& p, uint32_t BT, co
 {
     static const int enabled = [] { const char* v = getenv("SPX_CONV_RBM"); return v ? atoi(v) : 1; }();
     static const double share_env = [] { const char* v = getenv("SPX_CONV_RBM_MIN_SHARE"); return v ? atof(v) : -1.0; }();
+    if (e->tma_failed_host && *e->tma_failed_host) {
+        // reported once; the handle stages with per-thread copies from here on
+        *e->tma_failed_host = 0;
+        e->tma_off = true;
+        return fail(SPX_ERR_CUDA, "conv2d: a bulk tensor copy of an earlier call on this handle did not complete; its output is invalid");
+    }
     // fewer than 8 row blocks would leave most of the CTA's 16 warps without work
     if (!enabled || e->n > kRbmMaxK || e->m < 8 * kRbmRows - 3 || e->max_nnz == 0) return -1;
     const uint32_t bt = p.B % 16 == 0 ? 16 : BT;       // BT: the per-row kernel's batch tile for this batch

@@ -351,6 +351,10 @@ CONV_CASES = [
     (32, 8, 64, 56, 56, 3, 1, 1, 1), (32, 8, 64, 54, 50, 3, 1, 1, 1),
     # a last block of output channels that is not full (38 = 9 blocks of 4 + 2), batch tiles of 16 / 8 / 4
     (16, 6, 38, 10, 10, 3, 1, 1, 1), (8, 6, 38, 10, 10, 3, 1, 1, 1), (4, 6, 38, 10, 10, 3, 1, 1, 1),
+    # input channels staged in several chunks (the merged kernel double-buffers them): 70 channels
+    # end inside a chunk; stride 2, a 5x5 kernel and dilation change the staged patch's extent
+    (32, 70, 32, 12, 12, 3, 1, 1, 1), (16, 100, 38, 14, 14, 3, 2, 1, 1), (8, 64, 32, 12, 12, 5, 1, 2, 1),
+    (16, 96, 40, 13, 11, 3, 1, 2, 2),
 ]
 
 
@@ -417,8 +421,9 @@ def test_conv_unsorted_columns(lib, orc, cuda, layout):
     assert_bit_equal(dY.cpu().numpy(), want, "conv, unsorted columns")
 
 
-@pytest.mark.parametrize("env", [{"SPX_CONV_RBM": "0"}, {"SPX_CONV_RBM_MIN_SHARE": "0"}, {"SPX_CONV_DIRECT": "1"}],
-                         ids=["per-row-tiles", "row-block-merged", "direct"])
+@pytest.mark.parametrize("env", [{"SPX_CONV_RBM": "0"}, {"SPX_CONV_RBM_MIN_SHARE": "0"},
+                                 {"SPX_CONV_RBM_MIN_SHARE": "0", "SPX_CONV_TMA": "0"}, {"SPX_CONV_DIRECT": "1"}],
+                         ids=["per-row-tiles", "row-block-merged", "row-block-merged-cp-async", "direct"])
 def test_conv_each_kernel_forced(env):
     """The library picks a convolution kernel from batch size and density; the switches are read
     once per process, so each kernel is forced in a child process that reruns the conv parity cases."""
