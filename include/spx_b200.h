@@ -150,7 +150,10 @@ int spx_spmv_reference_order(const spx_ell* e, const float* x, const float* bias
  * and, on the device, build_rbm_from_ellpack (src/layers/rbm_conv.cpp:7-73): the first call per
  * handle and kernel shape builds and caches a tap table and, where the batch size and weight
  * density favour it, the row-block-merged form of the weights (device allocations; make that
- * call outside a stream capture).  Results do not depend on which kernel is chosen. */
+ * call outside a stream capture).  Results do not depend on which kernel is chosen.  The
+ * row-block-merged kernel fetches its input with bulk tensor copies and bounded waits; should a
+ * wait ever run out, the next spx_conv2d on the handle returns SPX_ERR_CUDA once (the output of
+ * the call that was in flight is invalid) and the handle falls back to per-thread copies. */
 int spx_conv2d(const spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
                const float* bias, int act, float* out, void* stream);
 /* spx_conv2d for callers that must not allocate device memory (no counterpart in the
