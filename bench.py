@@ -593,6 +593,7 @@ def measure(args, c):
     e2e_step = None
     ag_step = None
     fused_step = None
+    mcast_step, mcast_note, mbuf = None, None, None
     e2e_phases = None
     checks = []                 # (what, rows compared, ok) filled by run_checks after the timed regions
     run_checks = None
@@ -684,6 +685,27 @@ def measure(args, c):
                     lib.spx_spmm_bcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, parr, world,
                                        wk["row0"], C, stream)
                     lib.spx_comm_barrier(fcomm, stream)
+                # and through an NVLink multicast address (NVLS): the ranks' full buffers are one
+                # torch symmetric-memory allocation each, bound under one multicast address by the
+                # rendezvous; the epilogue stores every vector once (spx_spmm_mcast, multimem.st)
+                try:
+                    import torch.distributed._symmetric_memory as symm_mem
+                    mbuf = symm_mem.empty((wk["m"], C), dtype=torch.float32, device=dev)
+                    mhdl = symm_mem.rendezvous(mbuf, dist.group.WORLD.group_name)
+                    mc_ptr = int(mhdl.multicast_ptr or 0)
+                    all_mc = torch.tensor([1.0 if mc_ptr else 0.0], dtype=torch.float64, device=dev)
+                    dist.all_reduce(all_mc, op=dist.ReduceOp.MIN)
+                    if all_mc.item() != 1.0:
+                        mcast_note = "no multicast address from the symmetric-memory rendezvous on some rank"
+                        mc_ptr = 0
+                except Exception as ex:                      # every rank takes the same branch: the calls are collective
+                    mc_ptr, mbuf = 0, None
+                    mcast_note = f"symmetric memory unavailable: {type(ex).__name__}: {ex}"[:200]
+                if mc_ptr:
+                    def mcast_step():
+                        lib.spx_spmm_mcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, mc_ptr,
+                                           wk["row0"], C, stream)
+                        lib.spx_comm_barrier(fcomm, stream)
 
             def run_checks():
                 """After the timed regions: sampled rows of every result buffer against the oracle.
@@ -703,6 +725,8 @@ def measure(args, c):
                     fview = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
                     lib.spx_memcpy_d2d(fview.data_ptr(), fbuf, wk["m"] * C * 4, stream)
                     views.append(("fused-exchange Y", fview))
+                    if mcast_step is not None:
+                        views.append(("multicast-exchange Y", mbuf))
                     torch.cuda.synchronize()
                     for name, buf in views:
                         check_rows_against_oracle(buf[rows_lo + pick_dev], picked, name + ", own rows")
@@ -971,6 +995,16 @@ def measure(args, c):
         fused = {"ms_per_step": f_sec * 1e3, "value": to_value(wk, job_bytes, f_sec),
                  "note": "SpMM whose epilogue stores Y into every rank's full buffer over NVLink (peer stores) + barrier"}
 
+    mcast = None
+    if mcast_step is not None:
+        n_f = max(3, min(args.steps, 10))
+        m_sec = timed(mcast_step, n_f, 2, False) / n_f
+        mcast = {"ms_per_step": m_sec * 1e3, "value": to_value(wk, job_bytes, m_sec),
+                 "note": "SpMM whose epilogue stores Y once to an NVLink multicast address (multimem.st, replicated into "
+                         "every rank's full buffer by the NVSwitch) + barrier"}
+    elif mcast_note:
+        mcast = {"unavailable": mcast_note}
+
     check = None
     if run_checks is not None and not args.no_check:
         run_checks()
@@ -984,6 +1018,11 @@ def measure(args, c):
                  "buffers": [c[0] for c in checks], "failed": [c[0] for c in checks if not c[2]]}
         if not exact:
             check["tolerance"] = "1e-5 * (sum|w||x| + |bias|) per element" if kind == "spmv" else "1e-6 absolute on sigmoid outputs (chains before it are bit-identical)"
+
+    if mbuf is not None:
+        # nothing may still be storing to the multicast address when a rank lets go of its buffer
+        torch.cuda.synchronize()
+        dist.barrier()
 
     # Measured denominator for the SpMM operand path: random 512-byte gathers from an L2-resident
     # buffer, L1 bypassed (the bench-side probe library), timed here on this GPU right after the workload.
@@ -1050,6 +1089,8 @@ def measure(args, c):
             line["with_allgather"] = ag
         if fused:
             line["with_fused_allgather"] = fused
+        if mcast:
+            line["with_multicast_allgather"] = mcast
         if not args.no_cpu and world == 1:
             try:
                 run, frac, ckind, sample = cpu_sample_runner(args, wk, fraction=0.25 if args.workload == "cfg5_spmm" else None)

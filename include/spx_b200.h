@@ -242,6 +242,14 @@ int spx_ipc_close(void* dptr);
  * Same arithmetic as spx_spmm (the split is the row loop of src/ellpack_matmul.cpp:26). */
 int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
                    float* const* Ys, uint32_t nbuffers, uint64_t row_offset, uint64_t ldy, void* stream);
+/* The same with one destination: Ymc is an NVLink multicast address under which every rank's full
+ * Y buffer is bound (an NVLS multicast object; e.g. the multicast_ptr of a torch symmetric-memory
+ * rendezvous over those buffers).  Each finished vector leaves this GPU once (multimem.st) and the
+ * NVSwitch replicates it into all bound buffers, this rank's included: (G-1)x less traffic out of
+ * every GPU than spx_spmm_bcast.  C, ldx, ldy multiples of 4; X and Ymc 16-byte aligned.  Follow
+ * it with spx_comm_barrier before any rank reads Y. */
+int spx_spmm_mcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                   float* Ymc, uint64_t row_offset, uint64_t ldy, void* stream);
 
 #ifdef __cplusplus
 }

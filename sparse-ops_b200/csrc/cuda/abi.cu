@@ -460,6 +460,24 @@ int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, c
     return launch_spmm_bcast(e, X, C, ldx, bias, act, Ys, nbuffers, row_offset, ldy, (cudaStream_t)stream);
 }
 
+int spx_spmm_mcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                   float* Ymc, uint64_t row_offset, uint64_t ldy, void* stream)
+{
+    if (!e) return fail(SPX_ERR_ARG, "handle is null");
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (!Ymc) return fail(SPX_ERR_ARG, "multicast address is null");
+    if (e->m == 0 || C == 0) return SPX_OK;
+    if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
+    if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    // multimem.st needs naturally aligned 16-byte vectors: the library's scalar kernels would store
+    // single floats, which a multicast mapping also takes, but every shape is kept on one rule
+    if (C % 4 || ldx % 4 || ldy % 4 || (reinterpret_cast<uintptr_t>(Ymc) & 15) || (reinterpret_cast<uintptr_t>(X) & 15))
+        return fail(SPX_ERR_ARG, "spmm_mcast: C, ldx and ldy must be multiples of 4 and X, Ymc 16-byte aligned");
+    if (int rc = check_current_device(e, "spmm_mcast")) return rc;
+    float* one[1] = { Ymc };
+    return launch_spmm_bcast(e, X, C, ldx, bias, act, one, 1, row_offset, ldy, (cudaStream_t)stream, true);
+}
+
 int spx_ipc_export(void* dptr, char handle[SPX_IPC_HANDLE_BYTES])
 {
     static_assert(sizeof(cudaIpcMemHandle_t) == SPX_IPC_HANDLE_BYTES, "IPC handle size");

@@ -126,7 +126,7 @@ namespace spx {
 int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias,
                 int act, float* Y, uint64_t ldy, cudaStream_t s);
 int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
-                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s);
+                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s, bool mcast = false);
 int launch_spmv(spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
 int launch_spmv_reforder(const spx_ell* e, const float* x, const float* bias, float* y, cudaStream_t s);
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,

@@ -541,7 +541,9 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
     // zeros.  Every wait is bounded: after a wait that ran out the CTA stops waiting, finishes on
     // whatever the buffers hold, raises *tma_failed (the host then reports the call as failed) and
     // CTAs that start later leave at once.
-    const uint32_t box_bytes = tp.CC * tp.THin * tp.TWin * BT * (uint32_t)sizeof(float);
+    // use_tma bit 1 (a test switch): the barrier is told to expect 16 bytes more than the copy
+    // delivers, so the wait runs out and the failure report can be exercised without any fault.
+    const uint32_t box_bytes = tp.CC * tp.THin * tp.TWin * BT * (uint32_t)sizeof(float) + ((use_tma & 2u) ? 16u : 0u);
     bool landed = true;
     if (use_tma) {
         if (threadIdx.x == 0) {
@@ -785,7 +787,8 @@ static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32
         if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(in), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
-            use_tma = 1;
+            static const int short_env = [] { const char* v = getenv("SPX_CONV_TMA_TEST_TIMEOUT"); return v ? atoi(v) : 0; }();
+            use_tma = short_env ? 3u : 1u;
             tp.CC = cc;
             tp.stage = (uint32_t)((chanBytes * cc + 127) / 128 * 32);     // buffers start on 128-byte boundaries
         }

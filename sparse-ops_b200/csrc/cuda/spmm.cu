@@ -56,8 +56,32 @@ __device__ __forceinline__ void decode_block(const BlockMap& bm, uint32_t b, uin
 struct PeerOut {
     float* p[kMaxPeers];
     int n;
+    int mcast;          // p[0] is an NVLink multicast address: one multimem.st reaches every rank's buffer
     uint64_t row0;      // first row of this rank's slab inside the full buffers
 };
+
+// One finished vector to every destination.  Peer list: one ordinary 16-byte store per buffer (the
+// GPU sends the vector once per peer).  Multicast address: a single multimem.st, replicated to all
+// bound GPUs (this one included) by the NVSwitch, so the vector leaves this GPU once.
+__device__ __forceinline__ void store_out(const PeerOut& out, size_t at, const float4& o) {
+    if (out.mcast) {
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(out.p[0] + at), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+        return;
+    }
+#pragma unroll
+    for (int g = 0; g < kMaxPeers; ++g)
+        if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+}
+__device__ __forceinline__ void store_out(const PeerOut& out, size_t at, float o) {
+    if (out.mcast) {
+        asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(out.p[0] + at), "f"(o) : "memory");
+        return;
+    }
+#pragma unroll
+    for (int g = 0; g < kMaxPeers; ++g)
+        if (g < out.n) out.p[g][at] = o;
+}
 
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
@@ -138,9 +162,7 @@ spmm_gather_vec(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
             }
             const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 128 * v;
-#pragma unroll
-            for (int g = 0; g < kMaxPeers; ++g)
-                if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+            store_out(out, at, o);
         }
     }
 }
@@ -247,9 +269,7 @@ __device__ __forceinline__ void staged_row(const float* __restrict__ w, const ui
                 o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
             }
             const size_t at = out_at + 128 * v;
-#pragma unroll
-            for (int g = 0; g < kMaxPeers; ++g)
-                if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+            store_out(out, at, o);
         }
     }
 }
@@ -379,9 +399,7 @@ spmm_gather_sub(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
             o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
         }
         const size_t at = (size_t)(out.row0 + row) * ldy + c0;
-#pragma unroll
-        for (int g = 0; g < kMaxPeers; ++g)
-            if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+        store_out(out, at, o);
     }
 }
 
@@ -459,9 +477,7 @@ spmm_gather_half(const float* __restrict__ Wd, const uint32_t* __restrict__ idx,
                 o.z = spx::apply_act(o.z, act); o.w = spx::apply_act(o.w, act);
             }
             const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 64 * v;
-#pragma unroll
-            for (int g = 0; g < kMaxPeers; ++g)
-                if (g < out.n) *reinterpret_cast<float4*>(out.p[g] + at) = o;
+            store_out(out, at, o);
         }
     }
 }
@@ -529,9 +545,7 @@ spmm_gather_scalar(const float* __restrict__ Wd, const uint32_t* __restrict__ id
         if (on[v]) {
             const float o = spx::apply_act(acc[v], act);
             const size_t at = (size_t)(out.row0 + row) * ldy + c0 + 32 * v;
-#pragma unroll
-            for (int g = 0; g < kMaxPeers; ++g)
-                if (g < out.n) out.p[g][at] = o;
+            store_out(out, at, o);
         }
 }
 
@@ -614,12 +628,14 @@ int launch_spmm(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, cons
 }
 
 int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
-                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s)
+                      float* const* Ys, uint32_t npeers, uint64_t row0, uint64_t ldy, cudaStream_t s, bool mcast)
 {
     if (e->m == 0 || C == 0) return SPX_OK;
     if (npeers == 0 || npeers > (uint32_t)kMaxPeers) return fail(SPX_ERR_LIMIT, "spmm: 1..%d destination buffers supported", kMaxPeers);
+    if (mcast && npeers != 1) return fail(SPX_ERR_ARG, "spmm: a multicast destination is one address");
     PeerOut out{};
     out.n = (int)npeers;
+    out.mcast = mcast ? 1 : 0;
     out.row0 = row0;
     bool aligned = true;
     for (uint32_t g = 0; g < npeers; ++g) {
@@ -680,7 +696,7 @@ int launch_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx
             // idle until then; shortest first behind the head keeps them busy from the start, while
             // the long rows (the head) still start at once.  SPX_SPMM_BCAST_ORDER=0 keeps descending.
             static const int order_env = [] { const char* v = getenv("SPX_SPMM_BCAST_ORDER"); return v ? atoi(v) : 1; }();
-            sm.rest_ascending = (npeers > 1 && order_env) ? 1u : 0u;
+            sm.rest_ascending = ((npeers > 1 || mcast) && order_env) ? 1u : 0u;
             sm.row_blocks = (e->m + wpb - 1) / wpb;
             sm.panels = all_narrow ? (C + 127) / 128 : (C + 255) / 256;
             sm.head_panels = (C + 127) / 128;

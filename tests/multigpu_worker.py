@@ -129,6 +129,52 @@ def main():
     dist.barrier()
     lib.spx_free(buf)
 
+    # 1d. the exchange through an NVLink multicast address (NVLS): the full buffers are torch
+    # symmetric-memory allocations bound under one multicast address; every vector is stored once
+    # (multimem.st) and the switch replicates it.  Both matrices of 1b / 1c.  Reported as skipped
+    # when the rendezvous yields no multicast address on this machine.
+    mc_state = "skipped"
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        mbuf = symm_mem.empty((per * world, Cc), dtype=torch.float32, device=dev)
+        mhdl = symm_mem.rendezvous(mbuf, dist.group.WORLD.group_name)
+        mc_ptr = int(mhdl.multicast_ptr or 0)
+    except Exception as ex:
+        mc_ptr, mbuf = 0, None
+        mc_state = f"skipped ({type(ex).__name__})"
+    have = torch.tensor([1.0 if mc_ptr else 0.0], device=dev)
+    dist.all_reduce(have, op=dist.ReduceOp.MIN)
+    if have.item() == 1.0:
+        mbuf.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        lib.spx_spmm_mcast(h.h, dX.data_ptr(), Cc, Cc, dB.data_ptr(), sx.ACT_RELU, mc_ptr, rank * per, Cc, stream)
+        lib.spx_comm_barrier(comm, stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(mbuf.cpu().numpy()[:m].view(np.uint32), want.view(np.uint32)), "multicast exchange differs"
+        dist.barrier()
+        flat = mbuf.view(-1)
+        flat.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        lib.spx_spmm_mcast(h2.h, dX2.data_ptr(), Cw, Cw, dB2.data_ptr(), sx.ACT_NONE, mc_ptr, rank * per2, Cw, stream)
+        lib.spx_comm_barrier(comm, stream)
+        torch.cuda.synchronize()
+        gotm = flat[:per2 * world * Cw].view(per2 * world, Cw).cpu().numpy()
+        assert np.array_equal(gotm[:m2].view(np.uint32), want2.view(np.uint32)), "multicast exchange on a skewed matrix differs"
+        # misuse: a column count that is not a multiple of 4 is refused before any launch
+        try:
+            lib.spx_spmm_mcast(h.h, dX.data_ptr(), 95, Cc, dB.data_ptr(), sx.ACT_RELU, mc_ptr, rank * per, Cc, stream)
+            raise AssertionError("spx_spmm_mcast accepted C = 95")
+        except sx.SpxError as err:
+            assert err.status == 1
+        mc_state = "ok"
+        torch.cuda.synchronize()
+        dist.barrier()                               # no store in flight when the buffers go away
+    if rank == 0:
+        print(f"multicast exchange: {mc_state}")
+    mbuf = None
+
     # 4. host buffers, sharded copy of X: several 256-column panels (ragged last one) and a single panel
     for (m4, n4, C4) in ((1003, 701, 772), (64, 50, 36)):
         W4 = sparse(rng, m4, n4, 0.1)

@@ -437,6 +437,53 @@ def test_conv_each_kernel_forced(env):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
 
+def test_conv_bulk_copy_timeout_child(lib, orc, cuda):
+    """Body of test_conv_bulk_copy_timeout_is_reported; needs the switch set before the library loads."""
+    if os.environ.get("SPX_CONV_TMA_TEST_TIMEOUT") != "1":
+        pytest.skip("runs in a child process of test_conv_bulk_copy_timeout_is_reported")
+    B, Cin, Cout, H, W, k = 16, 40, 32, 12, 12, 3          # merged kernel, several channel chunks
+    rng = np.random.default_rng(5)
+    wt = sparse(rng, Cout, Cin * k * k, 0.25) * np.float32(0.3)
+    bias = rng.standard_normal(Cout).astype(np.float32)
+    x = rng.standard_normal((B, Cin, H, W)).astype(np.float32)
+    src = as_layout(x, sx.LAYOUT_PF)
+    E = orc.encode(wt)
+    gd = dict(Cin=Cin, kH=k, kW=k, sH=1, sW=1, pH=1, pW=1, dH=1, dW=1, H=H, W=W)
+    want = orc.conv2d(E, gd, sx.LAYOUT_PF, src, B, bias, 1)
+    h = gpu_ell(lib, E)
+    g = sx.conv_geom(Cin, Cout, k, k, H, W, 1, 1, 1, 1, 1, 1)
+    dX, dB = dev(src, cuda), dev(bias, cuda)
+    dY = torch.full(want.shape, float("nan"), device=cuda, dtype=torch.float32)
+    # 1st call: enqueued fine; on the GPU the barrier expects 16 bytes that never come, the wait
+    # gives up after a second and the kernel raises the handle's status word
+    h.conv2d(g, sx.LAYOUT_PF, ptr(dX), B, ptr(dB), sx.ACT_RELU, ptr(dY))
+    torch.cuda.synchronize()                               # the context is still usable
+    # 2nd call: reports it, once
+    with pytest.raises(sx.SpxError) as err:
+        h.conv2d(g, sx.LAYOUT_PF, ptr(dX), B, ptr(dB), sx.ACT_RELU, ptr(dY))
+    assert err.value.status == 2 and "bulk tensor copy" in str(err.value)
+    # 3rd call: the handle stages with per-thread copies from here on, results are right again
+    dY.fill_(float("nan"))
+    h.conv2d(g, sx.LAYOUT_PF, ptr(dX), B, ptr(dB), sx.ACT_RELU, ptr(dY))
+    torch.cuda.synchronize()
+    assert_bit_equal(dY.cpu().numpy(), want, "conv after the reported timeout")
+
+
+def test_conv_bulk_copy_timeout_is_reported():
+    """The merged kernel's wait for its bulk tensor copies is bounded.  With the test switch the
+    barrier expects more bytes than the copy delivers, so the wait runs out (nothing faults, nothing
+    hangs): the kernel returns, the next call on the handle fails with SPX_ERR_CUDA, the one after
+    works and is bit-exact."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+           os.path.join(here, "test_parity_gpu.py"), "-k", "bulk_copy_timeout_child"]
+    env = {**os.environ, "SPX_CONV_TMA_TEST_TIMEOUT": "1", "SPX_CONV_RBM_MIN_SHARE": "0"}
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "1 passed" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
+
+
 def test_conv_rejects_bad_geometry(lib, orc, cuda):
     E = orc.encode(np.ones((4, 18), np.float32))
     h = gpu_ell(lib, E)
