@@ -594,6 +594,7 @@ def measure(args, c):
     ag_step = None
     fused_step = None
     mcast_step, mcast_note, mbuf = None, None, None
+    exchange_step, xslices = None, 0
     e2e_phases = None
     checks = []                 # (what, rows compared, ok) filled by run_checks after the timed regions
     run_checks = None
@@ -685,6 +686,14 @@ def measure(args, c):
                     lib.spx_spmm_bcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, parr, world,
                                        wk["row0"], C, stream)
                     lib.spx_comm_barrier(fcomm, stream)
+                # the exchange through the copy engines: slices of the rank's rows go to the peers by
+                # asynchronous device-to-device copies while the next slices are multiplied
+                xslices = int(os.environ.get("SPX_BENCH_EXCHANGE_SLICES", "4"))
+
+                def exchange_step():
+                    lib.spx_spmm_exchange(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, parr, world,
+                                          rank, wk["row0"], C, xslices, stream)
+                    lib.spx_comm_barrier(fcomm, stream)
                 # and through an NVLink multicast address (NVLS): the ranks' full buffers are one
                 # torch symmetric-memory allocation each, bound under one multicast address by the
                 # rendezvous; the epilogue stores every vector once (spx_spmm_mcast, multimem.st)
@@ -722,9 +731,21 @@ def measure(args, c):
                     rp2, c2, v2 = wl.cfg5_rows(nb * wk["rows"], 4096, n=wk["n"], kmax=min(2048, wk["n"] // 2)) \
                         if args.workload == "cfg5_spmm" else (None, None, None)
                     views = [("NCCL-gathered Y", Yfull)]
-                    fview = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
-                    lib.spx_memcpy_d2d(fview.data_ptr(), fbuf, wk["m"] * C * 4, stream)
-                    views.append(("fused-exchange Y", fview))
+
+                    def shared_buffer_copy():
+                        v = torch.empty((wk["m"], C), device=dev, dtype=torch.float32)
+                        lib.spx_memcpy_d2d(v.data_ptr(), fbuf, wk["m"] * C * 4, stream)
+                        torch.cuda.synchronize()
+                        return v
+                    # the shared buffers hold what the last timed exchange wrote: the copy-engine one;
+                    # then they are overwritten with NaN patterns and the fused exchange runs once more
+                    views.append(("copy-engine-exchange Y", shared_buffer_copy()))
+                    dist.barrier()
+                    lib.spx_memset(fbuf, 0xff, wk["m"] * C * 4, stream)
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    fused_step()
+                    views.append(("fused-exchange Y", shared_buffer_copy()))
                     if mcast_step is not None:
                         views.append(("multicast-exchange Y", mbuf))
                     torch.cuda.synchronize()
@@ -1019,6 +1040,14 @@ def measure(args, c):
         if not exact:
             check["tolerance"] = "1e-5 * (sum|w||x| + |bias|) per element" if kind == "spmv" else "1e-6 absolute on sigmoid outputs (chains before it are bit-identical)"
 
+    xchg = None
+    if exchange_step is not None:
+        n_f = max(3, min(args.steps, 10))
+        x_sec = timed(exchange_step, n_f, 2, False) / n_f
+        xchg = {"ms_per_step": x_sec * 1e3, "value": to_value(wk, job_bytes, x_sec), "slices": xslices,
+                "note": "SpMM in row slices, each slice copied into every rank's full buffer by the copy engines over NVLink "
+                        "while the next slices are multiplied (spx_spmm_exchange) + barrier"}
+
     if mbuf is not None:
         # nothing may still be storing to the multicast address when a rank lets go of its buffer
         torch.cuda.synchronize()
@@ -1089,6 +1118,8 @@ def measure(args, c):
             line["with_allgather"] = ag
         if fused:
             line["with_fused_allgather"] = fused
+        if xchg:
+            line["with_copy_engine_allgather"] = xchg
         if mcast:
             line["with_multicast_allgather"] = mcast
         if not args.no_cpu and world == 1:

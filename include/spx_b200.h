@@ -242,6 +242,17 @@ int spx_ipc_close(void* dptr);
  * Same arithmetic as spx_spmm (the split is the row loop of src/ellpack_matmul.cpp:26). */
 int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
                    float* const* Ys, uint32_t nbuffers, uint64_t row_offset, uint64_t ldy, void* stream);
+/* The same exchange through the copy engines: the rank's rows are multiplied in `slices` (0 = 4,
+ * at most 16) contiguous slices of near-equal work on `stream`, each written into Ys[self]; as
+ * soon as a slice is final it is copied into every other buffer Ys[g] with asynchronous
+ * device-to-device copies on internal streams, so the NVLink transfer of slice k overlaps the
+ * multiplication of slices k+1.. and takes no load/store slots from the SMs.  `stream` continues
+ * once all copies are done (fork / join by events; works under stream capture after a first,
+ * uncaptured call has built the slices).  Follow it with spx_comm_barrier before any rank reads Y.
+ * Same arithmetic as spx_spmm. */
+int spx_spmm_exchange(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                      float* const* Ys, uint32_t nbuffers, uint32_t self, uint64_t row_offset, uint64_t ldy,
+                      uint32_t slices, void* stream);
 /* The same with one destination: Ymc is an NVLink multicast address under which every rank's full
  * Y buffer is bound (an NVLS multicast object; e.g. the multicast_ptr of a torch symmetric-memory
  * rendezvous over those buffers).  Each finished vector leaves this GPU once (multimem.st) and the

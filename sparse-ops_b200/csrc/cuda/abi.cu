@@ -394,6 +394,11 @@ int spx_ell_destroy(spx_ell* e)
 {
     if (!e) return SPX_OK;
     DeviceGuard g(e->device);
+    for (uint32_t k = 0; k < e->nslices; ++k) spx_ell_destroy(e->slices[k]);
+    e->nslices = 0;
+    if (e->view) e->Wd = nullptr, e->idx = nullptr, e->nnz = nullptr;      // the parent's arrays
+    for (cudaStream_t st : e->xchg_streams) if (st) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : e->xchg_events) if (ev) cudaEventDestroy(ev);
     cudaFree(e->Wd); cudaFree(e->idx); cudaFree(e->nnz); cudaFree(e->row_order); cudaFree(e->taps); cudaFree(e->spmv_split); cudaFree(e->rbm_hdr); cudaFree(e->rbm_w); cudaFree(e->rbm_ncols); cudaFree(e->stage_dev); cudaFree(e->conv_scratch); cudaFree(e->fm_scratch);
     if (e->tma_failed_host) cudaFreeHost(e->tma_failed_host);
     if (e->tma_failed_dev) cudaFree(e->tma_failed_dev);
@@ -458,6 +463,98 @@ int spx_spmm_bcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, c
     if (!X && e->nnz_total) return fail(SPX_ERR_ARG, "X is null");
     if (int rc = check_current_device(e, "spmm_bcast")) return rc;
     return launch_spmm_bcast(e, X, C, ldx, bias, act, Ys, nbuffers, row_offset, ldy, (cudaStream_t)stream);
+}
+
+// Cuts the handle's rows into `want` contiguous ranges of near-equal cost (stored entries + 8 per
+// row) and makes a view handle with its own row schedule for each.
+static int ensure_slices(spx_ell* e, uint32_t want)
+{
+    if (e->nslices == want) return SPX_OK;
+    for (uint32_t k = 0; k < e->nslices; ++k) spx_ell_destroy(e->slices[k]);
+    e->nslices = 0;
+    std::vector<uint32_t> nnz(e->m);
+    SPX_CUDA(cudaMemcpy(nnz.data(), e->nnz, (size_t)e->m * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    uint64_t total = 0;
+    for (uint32_t i = 0; i < e->m; ++i) total += nnz[i] + 8u;
+    uint32_t r0 = 0;
+    uint64_t acc = 0;
+    for (uint32_t k = 0; k < want; ++k) {
+        const uint64_t target = total * (k + 1) / want;
+        uint32_t r1 = r0;
+        while (r1 < e->m && (acc < target || k + 1 == want)) acc += nnz[r1++] + 8u;
+        spx_ell* v = new spx_ell();
+        v->device = e->device;
+        v->view = true;
+        v->m = r1 - r0; v->n = e->n; v->r = e->r; v->pitch = e->pitch;
+        v->Wd = e->Wd + (size_t)r0 * e->pitch;
+        v->idx = e->idx + (size_t)r0 * e->pitch;
+        v->nnz = e->nnz + r0;
+        v->cols_ascending = e->cols_ascending;
+        for (uint32_t i = r0; i < r1; ++i) {
+            v->nnz_total += nnz[i];
+            v->max_nnz = std::max(v->max_nnz, nnz[i]);
+        }
+        e->slices[k] = v;
+        e->slice_row0[k] = r0;
+        e->nslices = k + 1;
+        if (int rc = set_row_order(v, nnz.data() + r0)) return rc;
+        r0 = r1;
+    }
+    e->slice_row0[want] = e->m;
+    return SPX_OK;
+}
+
+int spx_spmm_exchange(const spx_ell* ce, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,
+                      float* const* Ys, uint32_t nbuffers, uint32_t self, uint64_t row_offset, uint64_t ldy,
+                      uint32_t slices, void* stream)
+{
+    if (!ce) return fail(SPX_ERR_ARG, "handle is null");
+    if (act < SPX_ACT_NONE || act > SPX_ACT_TANH) return fail(SPX_ERR_ARG, "unknown activation %d", act);
+    if (!Ys) return fail(SPX_ERR_ARG, "destination list is null");
+    if (nbuffers == 0 || nbuffers > 8 || self >= nbuffers) return fail(SPX_ERR_ARG, "spmm_exchange: 1..8 buffers, self among them");
+    for (uint32_t g = 0; g < nbuffers; ++g)
+        if (!Ys[g]) return fail(SPX_ERR_ARG, "spmm_exchange: destination %u is null", g);
+    if (slices == 0) slices = 4;
+    if (slices > 16) return fail(SPX_ERR_LIMIT, "spmm_exchange: at most 16 slices");
+    if (ce->m == 0 || C == 0) return SPX_OK;
+    if (ldx < C || ldy < C) return fail(SPX_ERR_ARG, "leading dimension smaller than C");
+    if (!X && ce->nnz_total) return fail(SPX_ERR_ARG, "X is null");
+    if (int rc = check_current_device(ce, "spmm_exchange")) return rc;
+    spx_ell* e = const_cast<spx_ell*>(ce);
+    slices = std::min(slices, e->m);
+    if (int rc = ensure_slices(e, slices)) return rc;
+    for (cudaStream_t& st : e->xchg_streams)
+        if (!st) SPX_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    for (cudaEvent_t& ev : e->xchg_events)
+        if (!ev) SPX_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaStream_t s = (cudaStream_t)stream;
+    float* own = Ys[self];
+    for (uint32_t k = 0; k < slices; ++k) {
+        const spx_ell* v = e->slices[k];
+        if (v->m == 0) continue;
+        const uint32_t r0 = e->slice_row0[k];
+        const size_t at = (size_t)(row_offset + r0) * ldy;
+        if (int rc = launch_spmm(v, X, C, ldx, bias ? bias + r0 : nullptr, act, own + at, ldy, s)) return rc;
+        if (nbuffers == 1) continue;
+        // the slice is final: hand it to the copy engines, one stream per peer modulo 4
+        SPX_CUDA(cudaEventRecord(e->xchg_events[k], s));
+        for (uint32_t g = 0; g < nbuffers; ++g) {
+            if (g == self) continue;
+            cudaStream_t cs = e->xchg_streams[g % 4];
+            SPX_CUDA(cudaStreamWaitEvent(cs, e->xchg_events[k], 0));
+            if (ldy == C)
+                SPX_CUDA(cudaMemcpyAsync(Ys[g] + at, own + at, (size_t)v->m * C * sizeof(float), cudaMemcpyDeviceToDevice, cs));
+            else
+                SPX_CUDA(cudaMemcpy2DAsync(Ys[g] + at, ldy * sizeof(float), own + at, ldy * sizeof(float), (size_t)C * sizeof(float),
+                                           v->m, cudaMemcpyDeviceToDevice, cs));
+        }
+    }
+    if (nbuffers > 1)
+        for (int i = 0; i < 4; ++i) {           // the caller's stream continues when every copy is done
+            SPX_CUDA(cudaEventRecord(e->xchg_events[16 + i], e->xchg_streams[i]));
+            SPX_CUDA(cudaStreamWaitEvent(s, e->xchg_events[16 + i], 0));
+        }
+    return SPX_OK;
 }
 
 int spx_spmm_mcast(const spx_ell* e, const float* X, uint32_t C, uint64_t ldx, const float* bias, int act,

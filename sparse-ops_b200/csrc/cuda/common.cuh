@@ -68,6 +68,16 @@ struct spx_ell {
     // that chain and time its stages, created on first use and kept.
     cudaStream_t pipe_streams[4] = {nullptr, nullptr, nullptr, nullptr};
     cudaEvent_t pipe_events[64] = {};
+    // Row slices for the copy-engine exchange (spx_spmm_exchange, abi.cu): handles over contiguous
+    // row ranges of this one that share its Wd / idx / nnz arrays and own only their row schedule
+    // (view == true for such a handle).  slice_row0[k] is slice k's first row; the streams carry
+    // the peer copies, the events chain them to the multiplications.
+    bool view = false;
+    uint32_t nslices = 0;
+    spx_ell* slices[16] = {};
+    uint32_t slice_row0[17] = {};
+    cudaStream_t xchg_streams[4] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t xchg_events[24] = {};
 };
 
 namespace spx {

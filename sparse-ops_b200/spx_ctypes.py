@@ -101,6 +101,8 @@ SIGNATURES = {
     "spx_ipc_close": (C.c_int, [_vp]),
     "spx_spmm_bcast": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint64, _vp, C.c_int, C.POINTER(_vp), C.c_uint32, C.c_uint64,
                                  C.c_uint64, _vp]),
+    "spx_spmm_exchange": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint64, _vp, C.c_int, C.POINTER(_vp), C.c_uint32, C.c_uint32,
+                                    C.c_uint64, C.c_uint64, C.c_uint32, _vp]),
     "spx_spmm_mcast": (C.c_int, [_vp, _vp, C.c_uint32, C.c_uint64, _vp, C.c_int, _vp, C.c_uint64, C.c_uint64, _vp]),
 }
 

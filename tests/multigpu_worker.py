@@ -123,6 +123,27 @@ def main():
     lib.spx_device_sync()
     want2 = orc.spmm(orc.encode(W2), X2, b2)
     assert np.array_equal(got2[:m2].view(np.uint32), want2.view(np.uint32)), "fused exchange on a skewed matrix differs"
+    # 1e. the exchange through the copy engines (spx_spmm_exchange): slices of the rank's rows are
+    # copied to the peers while the next slices are multiplied.  The skewed matrix in 3 slices, then
+    # the first matrix with a leading dimension wider than C (strided copies) in 5 slices.
+    lib.spx_memset(buf, 0xff, nbytes, 0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    lib.spx_spmm_exchange(h2.h, dX2.data_ptr(), Cw, Cw, dB2.data_ptr(), sx.ACT_NONE, arr, world, rank, rank * per2, Cw, 3, stream)
+    lib.spx_comm_barrier(comm, stream)
+    torch.cuda.synchronize()
+    lib.spx_memcpy_d2h(got2.ctypes.data_as(C.c_void_p), buf, got2.nbytes, 0)
+    lib.spx_device_sync()
+    assert np.array_equal(got2[:m2].view(np.uint32), want2.view(np.uint32)), "copy-engine exchange on a skewed matrix differs"
+    dist.barrier()
+    Cn = 64                                          # narrower than the leading dimensions
+    lib.spx_spmm_exchange(h.h, dX.data_ptr(), Cn, Cc, dB.data_ptr(), sx.ACT_RELU, arr, world, rank, rank * per, Cc, 5, stream)
+    lib.spx_comm_barrier(comm, stream)
+    torch.cuda.synchronize()
+    lib.spx_memcpy_d2h(got.ctypes.data_as(C.c_void_p), buf, nbytes, 0)
+    lib.spx_device_sync()
+    want_n = orc.spmm(orc.encode(W), np.ascontiguousarray(X[:, :Cn]), b, act=1)
+    assert np.array_equal(got[:m, :Cn].view(np.uint32), want_n.view(np.uint32)), "copy-engine exchange with ldy > C differs"
     dist.barrier()
     for pp in opened:
         lib.spx_ipc_close(pp)
