@@ -203,6 +203,48 @@ def test_spmm_bcast_into_two_buffers_long_rows(lib, orc, cuda, C):
         assert np.isnan(got[:row0]).all() and np.isnan(got[row0 + m:]).all()
 
 
+@pytest.mark.parametrize("C,slices,self_index", [(64, 3, 0), (260, 7, 1), (1024, 0, 0), (96, 16, 1)])
+def test_spmm_exchange_slices_into_two_buffers(lib, orc, cuda, C, slices, self_index):
+    """The SpMM in row slices whose finished slices the copy engines send to the other buffers
+    (the row-sharded exchange), here with two buffers on one GPU, a row offset and rows of 512 and
+    more entries; slices = 0 is the default of 4.  Both buffers against the oracle, bit for bit;
+    rows outside the shard stay untouched.  A second call with another slice count rebuilds the
+    slices; one buffer alone (no copies) works too."""
+    import ctypes as Ct
+    m, n, row0, total = 1500, 3000, 200, 2000
+    rng = np.random.default_rng([C, 78])
+    W = sparse(rng, m, n, 0.01)
+    for row, cnt in ((0, 700), (1, 513), (600, 3000), (1499, 1024)):
+        W[row] = 0
+        cols = rng.choice(n, cnt, replace=False)
+        W[row, cols] = rng.standard_normal(cnt).astype(np.float32)
+    X = rng.uniform(-1, 1, (n, C)).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    E = orc.encode(W)
+    h = gpu_ell(lib, E)
+    dX, dB = dev(X, cuda), dev(b, cuda)
+    want = orc.spmm(E, X, b, act=1)
+    stream = torch.cuda.current_stream().cuda_stream
+    for sl in (slices, 2):
+        bufs = [torch.full((total, C), float("nan"), device=cuda, dtype=torch.float32) for _ in range(2)]
+        arr = (Ct.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+        lib.spx_spmm_exchange(h.h, dX.data_ptr(), C, C, dB.data_ptr(), sx.ACT_RELU, arr, 2, self_index, row0, C, sl, stream)
+        torch.cuda.synchronize()
+        for i, buf in enumerate(bufs):
+            got = buf.cpu().numpy()
+            assert_bit_equal(got[row0:row0 + m], want, f"buffer {i}, {sl} slices")
+            assert np.isnan(got[:row0]).all() and np.isnan(got[row0 + m:]).all()
+    one = torch.full((total, C), float("nan"), device=cuda, dtype=torch.float32)
+    arr1 = (Ct.c_void_p * 1)(one.data_ptr())
+    lib.spx_spmm_exchange(h.h, dX.data_ptr(), C, C, dB.data_ptr(), sx.ACT_RELU, arr1, 1, 0, row0, C, 5, stream)
+    torch.cuda.synchronize()
+    assert_bit_equal(one.cpu().numpy()[row0:row0 + m], want, "one buffer")
+    with pytest.raises(sx.SpxError):
+        lib.spx_spmm_exchange(h.h, dX.data_ptr(), C, C, dB.data_ptr(), sx.ACT_RELU, arr, 2, 2, row0, C, 4, stream)   # self outside the list
+    with pytest.raises(sx.SpxError):
+        lib.spx_spmm_exchange(h.h, dX.data_ptr(), C, C, dB.data_ptr(), sx.ACT_RELU, arr, 2, 0, row0, C, 17, stream)  # too many slices
+
+
 @pytest.mark.parametrize("env", [{"SPX_SPMM_STAGED": "0"}, {"SPX_SPMM_STAGED": "1"}], ids=["gather_vec", "gather_staged"])
 def test_spmm_each_wide_kernel_forced(env):
     """Wide X with long rows runs on one of two kernels, chosen by an estimate of whether the longest
