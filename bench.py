@@ -698,6 +698,8 @@ def measure(args, c):
                 # torch symmetric-memory allocation each, bound under one multicast address by the
                 # rendezvous; the epilogue stores every vector once (spx_spmm_mcast, multimem.st)
                 try:
+                    if os.environ.get("SPX_BENCH_NO_MCAST") == "1":
+                        raise RuntimeError("switched off by SPX_BENCH_NO_MCAST")
                     import torch.distributed._symmetric_memory as symm_mem
                     mbuf = symm_mem.empty((wk["m"], C), dtype=torch.float32, device=dev)
                     mhdl = symm_mem.rendezvous(mbuf, dist.group.WORLD.group_name)
