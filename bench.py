@@ -704,14 +704,17 @@ def measure(args, c):
                     mbuf = symm_mem.empty((wk["m"], C), dtype=torch.float32, device=dev)
                     mhdl = symm_mem.rendezvous(mbuf, dist.group.WORLD.group_name)
                     mc_ptr = int(mhdl.multicast_ptr or 0)
-                    all_mc = torch.tensor([1.0 if mc_ptr else 0.0], dtype=torch.float64, device=dev)
-                    dist.all_reduce(all_mc, op=dist.ReduceOp.MIN)
-                    if all_mc.item() != 1.0:
-                        mcast_note = "no multicast address from the symmetric-memory rendezvous on some rank"
-                        mc_ptr = 0
-                except Exception as ex:                      # every rank takes the same branch: the calls are collective
+                    if not mc_ptr:
+                        mcast_note = "the symmetric-memory rendezvous gave no multicast address"
+                except Exception as ex:
                     mc_ptr, mbuf = 0, None
                     mcast_note = f"symmetric memory unavailable: {type(ex).__name__}: {ex}"[:200]
+                # every rank takes part in this reduction whatever happened above, and all take the same branch after it
+                all_mc = torch.tensor([1.0 if mc_ptr else 0.0], dtype=torch.float64, device=dev)
+                dist.all_reduce(all_mc, op=dist.ReduceOp.MIN)
+                if all_mc.item() != 1.0:
+                    mc_ptr = 0
+                    mcast_note = mcast_note or "no multicast address on another rank"
                 if mc_ptr:
                     def mcast_step():
                         lib.spx_spmm_mcast(ell.h, dX.data_ptr(), C, C, 0 if dB is None else dB.data_ptr(), sx.ACT_NONE, mc_ptr,
@@ -1050,7 +1053,7 @@ def measure(args, c):
                 "note": "SpMM in row slices, each slice copied into every rank's full buffer by the copy engines over NVLink "
                         "while the next slices are multiplied (spx_spmm_exchange) + barrier"}
 
-    if mbuf is not None:
+    if mcast_step is not None:                  # the same on every rank (decided by an all-reduce)
         # nothing may still be storing to the multicast address when a rank lets go of its buffer
         torch.cuda.synchronize()
         dist.barrier()
