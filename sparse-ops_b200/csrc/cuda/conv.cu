@@ -578,18 +578,32 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
             stage_chunk<QB, NB>(tile, tp, in, c0, c1, ih0, iw0, b0, warp, lane);
         }
         if (active) {
+            // lane l holds union column pos + l: header (packed tap, row mask) and its 4 weights.  The
+            // operands of the next batch of 32 columns are asked for before this batch's FMAs, so the
+            // round trip to L2 runs behind them.
+            bool have = pos + lane < nn;
+            uint2 h = make_uint2(0u, 0u);
+            float4 wl = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (have) {
+                h = __ldg(hrow + pos + lane);
+                wl = __ldg(wrow + pos + lane);
+            }
             for (;;) {
-                // lane l preloads union column pos + l: shared-memory offset << 8 | row mask, and its 4 weights
-                uint32_t hl = 0, cin = 0xffffffffu;
-                float4 wl = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (pos + lane < nn) {
-                    const uint2 h = __ldg(hrow + pos + lane);
-                    cin = h.x >> 16;
-                    const uint32_t tl = (((cin - c0) * tp.THin + ((h.x >> 8) & 0xffu) * p.dH) * tp.TWin + (h.x & 0xffu) * p.dW) * BT;
-                    hl = (tl << 8) | h.y;
-                    wl = __ldg(wrow + pos + lane);
-                }
+                const uint32_t cin = have ? (h.x >> 16) : 0xffffffffu;
+                const uint32_t tl = (((cin - c0) * tp.THin + ((h.x >> 8) & 0xffu) * p.dH) * tp.TWin + (h.x & 0xffu) * p.dW) * BT;
+                const uint32_t hl = (tl << 8) | h.y;      // shared-memory offset << 8 | row mask (unused beyond cnt)
                 const uint32_t cnt = __popc(__ballot_sync(0xffffffffu, cin < c1));   // a prefix: columns ascend
+                const uint32_t npos = pos + cnt;
+                bool nhave = false;
+                uint2 nh = make_uint2(0u, 0u);
+                float4 nw = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (cnt == 32) {
+                    nhave = npos + lane < nn;
+                    if (nhave) {
+                        nh = __ldg(hrow + npos + lane);
+                        nw = __ldg(wrow + npos + lane);
+                    }
+                }
                 for (uint32_t t = 0; t < cnt; ++t) {
                     const uint32_t hm = __shfl_sync(0xffffffffu, hl, t);
                     const float* xs = cur + (hm >> 8);
@@ -601,8 +615,9 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
                     rbm_row<2, G>(acc, hm, wl.z, t, x);
                     rbm_row<3, G>(acc, hm, wl.w, t, x);
                 }
-                pos += cnt;
+                pos = npos;
                 if (cnt < 32) break;
+                have = nhave; h = nh; wl = nw;
             }
         }
         __syncthreads();
