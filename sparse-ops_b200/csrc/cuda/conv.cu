@@ -498,6 +498,8 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
 {
     extern __shared__ __align__(128) float tile[];
     __shared__ __align__(8) uint64_t tile_bar[2];
+    __shared__ uint32_t buf_done[2];      // warps that have finished the chunk held by buffer 0 / 1
+    __shared__ uint32_t copies_asked;     // bulk copies this CTA has asked for
     constexpr int RB = (int)kRbmRows;
     constexpr uint32_t BT = QB * 4;
     constexpr uint32_t TH = 32u * G / QB / kTileW;       // rows of output positions per tile
@@ -534,44 +536,47 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
     const uint2* __restrict__ hrow = hdr + (size_t)(active ? blk : 0) * cap;
     const float4* __restrict__ wrow = w4 + (size_t)(active ? blk : 0) * cap;
     uint32_t pos = 0;
-    // Bulk-copy staging: two buffers of tp.CC channels each.  Thread 0 asks the copy unit for the
-    // next chunk's box before the CTA starts on the current one, so the fetch overlaps the
-    // arithmetic; the unit writes shared memory itself (no load / store slots of the 16 warps) and
-    // fills the halo with zeros.  A box always has tp.CC channels; past the last channel it reads
-    // zeros.  Every wait is bounded: after a wait that ran out the CTA stops waiting, finishes on
-    // whatever the buffers hold, raises *tma_failed (the host then reports the call as failed) and
-    // CTAs that start later leave at once.
+    // Bulk-copy staging: two buffers of tp.CC channels each, filled by the copy unit (no load / store
+    // slots of the 16 warps; the halo is the unit's zero fill; a box always has tp.CC channels, past
+    // the last channel it reads zeros).  Chunks 0 and 1 are asked for at once.  A warp waits on the
+    // buffer's mbarrier, multiplies, and counts itself out of the buffer; the warp that counts out
+    // last asks for the chunk after next into that buffer.  So the warps of a CTA never meet at a
+    // barrier: a warp with few columns in a chunk runs ahead into the next one.  Every wait is
+    // bounded: after a wait that ran out the warp stops waiting, finishes on whatever the buffers
+    // hold and raises *tma_failed (the host then reports the call as failed); no more copies are
+    // asked for and CTAs that start later leave at once.
     // use_tma bit 1 (a test switch): the barrier is told to expect 16 bytes more than the copy
     // delivers, so the wait runs out and the failure report can be exercised without any fault.
     const uint32_t box_bytes = tp.CC * tp.THin * tp.TWin * BT * (uint32_t)sizeof(float) + ((use_tma & 2u) ? 16u : 0u);
+    const uint32_t nchunks = (p.Cin + tp.CC - 1) / tp.CC;
+    const uint32_t blocks_left = (p.Cout - min(p.Cout, by * NB * RB) + RB - 1) / RB;
+    const uint32_t nactive = min((uint32_t)NB, blocks_left);       // warps of this CTA with rows
     bool landed = true;
     if (use_tma) {
         if (threadIdx.x == 0) {
             mbar_init(&tile_bar[0], 1);
             mbar_init(&tile_bar[1], 1);
+            buf_done[0] = 0;
+            buf_done[1] = 0;
+            copies_asked = min(2u, nchunks);
         }
         if (__syncthreads_or(*reinterpret_cast<volatile int*>(tma_failed) != 0)) return;
         if (threadIdx.x == 0) {
             mbar_expect_tx(&tile_bar[0], box_bytes);
             tma_load_4d(tile, &tmap, (int)b0, iw0, ih0, 0, &tile_bar[0]);
+            if (nchunks > 1) {
+                mbar_expect_tx(&tile_bar[1], box_bytes);
+                tma_load_4d(tile + tp.stage, &tmap, (int)b0, iw0, ih0, (int)tp.CC, &tile_bar[1]);
+            }
         }
+        if (!active) return;        // warps without rows take no part in the counting below
     }
-    uint32_t issued = 1;        // copies thread 0 has asked for
 
     uint32_t chunk = 0;
     for (uint32_t c0 = 0; c0 < p.Cin; c0 += tp.CC, ++chunk) {
         const uint32_t c1 = min(p.Cin, c0 + tp.CC);
         const float* cur = tile;
         if (use_tma) {
-            const uint32_t nb = (chunk + 1) & 1u;
-            if (threadIdx.x == 0 && c1 < p.Cin && landed) {
-                // buffer nb was last read for chunk - 1; the barrier that ended that chunk ordered
-                // those reads before this point, the fence orders them before the unit's writes
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_expect_tx(&tile_bar[nb], box_bytes);
-                tma_load_4d(tile + nb * tp.stage, &tmap, (int)b0, iw0, ih0, (int)c1, &tile_bar[nb]);
-                ++issued;
-            }
             if (landed) landed = mbar_wait(&tile_bar[chunk & 1u], (chunk >> 1) & 1u);
             cur = tile + (chunk & 1u) * tp.stage;
         } else {
@@ -620,16 +625,36 @@ conv_rbm_tile_kernel(const uint2* __restrict__ hdr, const float4* __restrict__ w
                 have = nhave; h = nh; wl = nw;
             }
         }
-        __syncthreads();
+        if (!use_tma) {
+            __syncthreads();
+            continue;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            const uint32_t b = chunk & 1u;
+            __threadfence_block();                                  // this warp's reads of the buffer, then the count
+            if (atomicAdd(&buf_done[b], 1u) + 1u == nactive) {      // last warp out of the buffer
+                buf_done[b] = 0;                                    // next counted out after the refill has landed
+                if (landed && chunk + 2 < nchunks) {
+                    __threadfence_block();
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // all warps' reads, then the unit's writes
+                    mbar_expect_tx(&tile_bar[b], box_bytes);
+                    tma_load_4d(tile + b * tp.stage, &tmap, (int)b0, iw0, ih0, (int)((chunk + 2) * tp.CC), &tile_bar[b]);
+                    atomicAdd(&copies_asked, 1u);
+                }
+            }
+        }
     }
     if (use_tma && !landed) {
         *tma_failed = 1;
         *tma_failed_host = 1;
         // the last two copies asked for may still be writing this CTA's shared memory: one more
-        // bounded wait for each before the CTA gives the memory up
-        if (threadIdx.x == 0)
-            for (uint32_t j = issued > 2 ? issued - 2 : 0; j < issued; ++j)
+        // bounded wait for each before this warp leaves (the memory stays until the last warp has)
+        if (lane == 0) {
+            const uint32_t asked = *reinterpret_cast<volatile uint32_t*>(&copies_asked);
+            for (uint32_t j = asked > 2 ? asked - 2 : 0; j < asked; ++j)
                 (void)mbar_wait(&tile_bar[j & 1u], (j >> 1) & 1u);
+        }
     }
     if (!active) return;
 #pragma unroll
