@@ -795,7 +795,7 @@ static PFN_cuTensorMapEncodeTiled tensor_map_encoder()
 
 template <int QB, int G>
 static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32_t ctas, const float* in, const float* bias,
-                            int act, float* out, cudaStream_t s)
+                            int act, float* out, cudaStream_t s, uint32_t b_avail)
 {
     constexpr int NB = 16;
     const ConvParams& p = tp.c;
@@ -820,7 +820,7 @@ static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32
         p.B % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
         // two buffers: half the channels of the single-buffer chunk each
         const uint32_t cc = std::min<uint32_t>(std::max<uint32_t>(1u, (uint32_t)(budget / 2 / chanBytes)), std::min<uint32_t>(p.Cin, 256));
-        const cuuint64_t gdim[4] = {p.B, p.W, p.H, p.Cin};
+        const cuuint64_t gdim[4] = {b_avail, p.W, p.H, p.Cin};    // `in` may point into the batch row (a segment)
         const cuuint64_t gstr[3] = {(cuuint64_t)p.B * 4, (cuuint64_t)p.W * p.B * 4, (cuuint64_t)p.H * p.W * p.B * 4};
         const cuuint32_t box[4] = {tp.BT, tp.TWin, tp.THin, cc};
         const cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -845,8 +845,13 @@ static int launch_rbm_units(const spx_ell* e, TileParams tp, RbmUnits un, uint32
 
 template <int QB>
 static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float* bias, int act, float* out,
-                         cudaStream_t s)
+                         cudaStream_t s, uint32_t b_base, uint32_t b_len)
 {
+    // a batch segment [b_base, b_base + b_len): the batch is the innermost dimension of both tensors,
+    // so the segment is the same kernel on pointers moved by b_base entries
+    in += b_base;
+    out += b_base;
+    const uint32_t b_avail = tp.c.B - b_base;       // batch entries from the moved pointer to the end of a row
     constexpr int NB = 16;
     const ConvParams& p = tp.c;
     constexpr uint32_t TH = 32u * kRbmG / QB / kTileW;
@@ -856,7 +861,7 @@ static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float
     const uint64_t tiles = (uint64_t)tp.tilesX * ((p.Ho + TH - 1) / TH);
     const uint32_t nblocks = (p.Cout + kRbmRows - 1) / kRbmRows;
     const uint32_t groups = (nblocks + NB - 1) / NB;
-    const uint64_t units = tiles * groups * (p.B / (QB * 4));
+    const uint64_t units = tiles * groups * (b_len / (QB * 4));
     if (units > 0x3fffffffull) return -1;
     const int rc = ensure_rbm(e, p.kH, p.kW, s);
     if (rc != SPX_OK) return rc;                        // -1: no memory for the merged weights
@@ -869,24 +874,26 @@ static int launch_rbm_qb(spx_ell* e, TileParams tp, const float* in, const float
     const uint32_t rem = (uint32_t)(units % sms);
     RbmUnits un{0u, (uint32_t)tiles, groups};
     if (split_tail && units > sms && rem && rem * 2 <= sms) {
-        const int rc1 = launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)(units - rem), in, bias, act, out, s);
+        const int rc1 = launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)(units - rem), in, bias, act, out, s, b_avail);
         if (rc1 != SPX_OK) return rc1;
         un.unit0 = (uint32_t)(units - rem);
-        return launch_rbm_units<QB, kRbmG / 2>(e, tp, un, rem * 2, in, bias, act, out, s);
+        return launch_rbm_units<QB, kRbmG / 2>(e, tp, un, rem * 2, in, bias, act, out, s, b_avail);
     }
-    return launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)units, in, bias, act, out, s);
+    return launch_rbm_units<QB, kRbmG>(e, tp, un, (uint32_t)units, in, bias, act, out, s, b_avail);
 }
 
-// Row-block-merged path.  Taken whenever K fits the builder's set and the batch tile is 16 (any
-// batch that is a multiple of 16), 8 or 4.  Measured against conv_pf_tile_kernel on 256 -> 256
+// Row-block-merged path.  Taken whenever K fits the builder's set and the batch is a multiple of 4:
+// multiples of 16 on tiles of 16 entries, the rest on a tile of 8 and / or of 4, each segment a
+// launch of its own on pointers moved along the (innermost) batch dimension (batch 20 / 24 / 12:
+// 1.00 / 1.16 / 0.68 ms against 1.39 / 1.59 / 0.76 ms on the per-row kernel's tiles of 20 / 24 /
+// 12).  Measured against conv_pf_tile_kernel on 256 -> 256
 // channels, 3 x 3, 56 x 56 (ms, merged vs per-row):
 //   batch 32 (tiles of 16; faster than tiles of 32: twice the channels per staged chunk):
 //     dense 4.1 vs 7.9, 50 % sparse 2.77 vs 4.15, 80 % 1.69 vs 1.89, 90 % 1.07 vs 1.13,
 //     95 % 0.69 vs 0.75, 99 % 0.35 vs 0.44;
 //   batch 8: 80 % 0.51 vs 0.57, 90 % 0.33 vs 0.40, 99 % 0.12 vs 0.25;   batch 4: 90 % 0.26 vs 0.37.
 // The fewer operand loads pay at high density; at low density the win comes from a CTA covering 64
-// output channels per staged chunk instead of 16 or 32.  Other batch sizes (tiles of 12, 20, 24,
-// 28) keep the per-row kernel with its wider batch tile.  SPX_CONV_RBM=0 turns the path off;
+// output channels per staged chunk instead of 16 or 32.  SPX_CONV_RBM=0 turns the path off;
 // SPX_CONV_RBM_MIN_SHARE=x requires an expected 4 d / (1 - (1 - d)^4) >= x rows per union column
 // (density d).  Returns -1 when not taken.
 static int launch_conv_rbm_tile(spx_ell* e, const ConvParams& p, uint32_t BT, const float* in, const float* bias,
@@ -902,16 +909,45 @@ static int launch_conv_rbm_tile(spx_ell* e, const ConvParams& p, uint32_t BT, co
     }
     // fewer than 8 row blocks would leave most of the CTA's 16 warps without work
     if (!enabled || e->n > kRbmMaxK || e->m < 8 * kRbmRows - 3 || e->max_nnz == 0) return -1;
-    const uint32_t bt = p.B % 16 == 0 ? 16 : BT;       // BT: the per-row kernel's batch tile for this batch
-    if (bt != 16 && bt != 8 && bt != 4) return -1;
+    (void)BT;
+    if (p.B % 4) return -1;
     const double d = (double)e->nnz_total / ((double)e->m * e->n);
     const double share = d >= 1.0 ? (double)kRbmRows : kRbmRows * d / (1.0 - std::pow(1.0 - d, (double)kRbmRows));
     if (share_env >= 0.0 && share < share_env) return -1;
+    // The batch in segments: all multiples of 16 on tiles of 16 entries, then a tile of 8 and / or
+    // of 4 for the rest, one launch (or two, with the tail split) per segment.  Batch 8 keeps its
+    // single tile of 8.  SPX_CONV_RBM_SEGMENTS=0: only batches that are one tile of 4 / 8 or a
+    // multiple of 16, the others on the per-row kernel.
+    static const int segments = [] { const char* v = getenv("SPX_CONV_RBM_SEGMENTS"); return v ? atoi(v) : 1; }();
+    const uint32_t n16 = p.B / 16 * 16, rest = p.B - n16;
+    if (!segments && n16 && rest) return -1;
+    if (!segments && !n16 && rest == 12) return -1;
+    // every segment's staged patch must fit shared memory (checked before any launch)
+    const auto fits = [&](uint32_t qb) {
+        const uint32_t TH = 32u * kRbmG / qb / kTileW;
+        const size_t THin = (size_t)(TH - 1) * p.sH + (size_t)(p.kH - 1) * p.dH + 1;
+        const size_t TWin = (size_t)(kTileW - 1) * p.sW + (size_t)(p.kW - 1) * p.dW + 1;
+        return THin * TWin * qb * 4 * sizeof(float) <= 200 * 1024;
+    };
+    if ((n16 && !fits(4)) || (rest >= 8 && !fits(2)) || (rest % 8 == 4 && !fits(1))) return -1;
     TileParams tp{};
     tp.c = p;
-    if (bt == 16) return launch_rbm_qb<4>(e, tp, in, bias, act, out, s);
-    if (bt == 8) return launch_rbm_qb<2>(e, tp, in, bias, act, out, s);
-    return launch_rbm_qb<1>(e, tp, in, bias, act, out, s);
+    uint32_t at = 0;
+    if (n16) {
+        const int rc = launch_rbm_qb<4>(e, tp, in, bias, act, out, s, 0, n16);
+        if (rc != SPX_OK) return rc;
+        at = n16;
+    }
+    if (rest >= 8) {
+        const int rc = launch_rbm_qb<2>(e, tp, in, bias, act, out, s, at, 8);
+        if (rc != SPX_OK) return at ? fail(SPX_ERR_CUDA, "conv2d: a batch segment could not be launched") : rc;
+        at += 8;
+    }
+    if (p.B - at == 4) {
+        const int rc = launch_rbm_qb<1>(e, tp, in, bias, act, out, s, at, 4);
+        if (rc != SPX_OK) return at ? fail(SPX_ERR_CUDA, "conv2d: a batch segment could not be launched") : rc;
+    }
+    return SPX_OK;
 }
 
 // Returns -1 when the shape is not covered (caller falls back to the direct kernel).
@@ -979,20 +1015,31 @@ static int launch_conv_pf_tile(spx_ell* e, const ConvParams& p, const float* in,
 }
 
 // Batch size the tiled kernels run at: B rounded up to a multiple of 4, or further up to a multiple
-// of 16 when that is cheaper.  Cost per batch entry by the batch tile the kernels would pick,
-// measured on 256 -> 256 channels, 3 x 3, 56 x 56, 80 % sparse (ms per entry): tile 16 (merged
-// kernel) 0.056, tile 8 (merged) 0.064, tile 4 (merged) 0.094, per-row tiles of 12 / 20 / 24 / 28:
-// 0.064 / 0.069 / 0.066 / 0.068.  So 28 runs as 32 (1.83 against 1.91 ms with the widening passes)
-// and 44 as 48 (about 2.7 against 4.1 ms), while 12, 20, 24 and 36 stay as they are.
-static uint32_t padded_batch(uint32_t B)
+// of 16 when that is cheaper.  Cost per batch entry on 256 -> 256 channels, 3 x 3, 56 x 56, 80 %
+// sparse (ms per entry).  Merged kernel, which takes any multiple of 4 in segments of 16 / 8 / 4:
+// 0.0436 / 0.0516 / 0.0645 - rounding up to 16 never pays (28 as 16 + 8 + 4: 1.37 ms, as 32 with
+// the widening passes: 1.53 ms).  Per-row kernel (matrices the merged one does not take) with its
+// tiles of 4 .. 32: 0.094, 0.064, 0.064, 0.056, 0.069, 0.066, 0.068, 0.056 - there 28 runs as 32
+// and 44 as 48, while 12, 20, 24 and 36 stay as they are.
+static uint32_t padded_batch(uint32_t B, bool merged)
 {
     const uint32_t b4 = round_up(B, 4u), b16 = round_up(B, 16u);
-    if (b4 == b16) return b4;
+    if (b4 == b16 || merged) return b4;
     uint32_t tile = 0;
     for (uint32_t c = 32; c >= 4; c -= 4) if (b4 % c == 0) { tile = c; break; }
     static const double per_entry[9] = {0, 0.094, 0.064, 0.064, 0.056, 0.069, 0.066, 0.068, 0.056};
     const double as_is = b4 * per_entry[tile / 4], widened = b16 * 0.056 * 1.03;
     return widened < as_is ? b16 : b4;
+}
+
+// Whether launch_conv_rbm_tile will take this handle (the part of its test that does not depend on
+// the geometry): the merged kernel is on, K fits its builder, and there are at least 8 row blocks.
+static bool merged_kernel_takes(const spx_ell* e)
+{
+    static const int enabled = [] { const char* v = getenv("SPX_CONV_RBM"); return v ? atoi(v) : 1; }();
+    static const int segments = [] { const char* v = getenv("SPX_CONV_RBM_SEGMENTS"); return v ? atoi(v) : 1; }();
+    static const bool share_set = getenv("SPX_CONV_RBM_MIN_SHARE") != nullptr;
+    return enabled && segments && !share_set && e->cols_ascending && e->n <= kRbmMaxK && e->m >= 8 * kRbmRows - 3 && e->max_nnz != 0;
 }
 
 int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* in, uint32_t B,
@@ -1014,7 +1061,7 @@ int launch_conv2d(spx_ell* e, const spx_conv_geom* g, int layout, const float* i
     //     (256 -> 256 channels, 56 x 56: batch 3 takes 0.4 ms this way against 1.2 ms with the general
     //     kernel, batch 1 0.4 against 0.43 ms).
     // Arithmetic per output element is unchanged in both cases.
-    const uint32_t B4 = padded_batch(B);
+    const uint32_t B4 = padded_batch(B, merged_kernel_takes(e));
     ConvParams p4 = p;
     p4.B = B4;
     // F-major tensors, b + B*(c + C*(h + H*w)): [W,H,C,B] is [C,H,W,B] with the three outer

@@ -397,6 +397,9 @@ CONV_CASES = [
     # end inside a chunk; stride 2, a 5x5 kernel and dilation change the staged patch's extent
     (32, 70, 32, 12, 12, 3, 1, 1, 1), (16, 100, 38, 14, 14, 3, 2, 1, 1), (8, 64, 32, 12, 12, 5, 1, 2, 1),
     (16, 96, 40, 13, 11, 3, 1, 2, 2),
+    # batches that the merged kernel runs in segments: 16 + 8, 16 + 4, 8 + 4, 32 + 8 + 4, 16 + 8 + 4
+    (24, 12, 40, 10, 10, 3, 1, 1, 1), (20, 40, 32, 9, 12, 3, 1, 1, 1), (12, 8, 36, 10, 10, 3, 2, 1, 1),
+    (44, 6, 32, 8, 8, 3, 1, 1, 1), (28, 10, 33, 7, 9, 3, 1, 1, 1),
 ]
 
 
